@@ -1,0 +1,76 @@
+// Shared helpers for every kernel file of the library: element types, error
+// reporting to the host, and fixed-order reductions.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace mdma {
+
+// Element type codes shared with the Python side.
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// The last error of this library, as text.  Every exported function returns 0
+// on success and non-zero after storing a message here.
+inline char* error_buffer() {
+    static char buf[1024] = {0};
+    return buf;
+}
+inline int fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error_buffer(), 1024, fmt, ap);
+    va_end(ap);
+    return 1;
+}
+#define MDMA_REQUIRE(cond, ...) \
+    do { if (!(cond)) return ::mdma::fail(__VA_ARGS__); } while (0)
+#define MDMA_LAUNCH_OK(name) \
+    do { cudaError_t e_ = cudaGetLastError(); \
+         if (e_ != cudaSuccess) return ::mdma::fail("%s: launch failed: %s", name, cudaGetErrorString(e_)); } while (0)
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Sum over a warp; every lane gets the same value, and the order of additions
+// is fixed (butterfly), so the result does not depend on what else runs.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads, fixed order.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarps; ++w) total += scratch[w];
+    return total;
+}
+
+}  // namespace mdma
+
+// Dispatch on an element type code.
+#define MDMA_DISPATCH_DTYPE(code, T, ...)                                  \
+    do {                                                                   \
+        if ((code) == ::mdma::kF32) { using T = float; __VA_ARGS__; }      \
+        else if ((code) == ::mdma::kBF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else return ::mdma::fail("unknown dtype code %d", (int)(code));    \
+    } while (0)

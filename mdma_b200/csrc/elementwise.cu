@@ -1,0 +1,161 @@
+// Embedding gather, RMSNorm, rotary position encoding fused with the cache
+// write, and row gathers.  Every kernel is a template over the activation
+// type (float for the true 32-bit engine, bfloat16 for the serving engine);
+// sums of squares, rotation angles and their sines are always float.
+#include "common.cuh"
+
+namespace mdma {
+
+// ---------------------------------------------------------------- embedding
+// x[t,:] = float(table[ids[t],:]).  The residual stream is float in both engines.
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                  float* __restrict__ out, int width, int vocab) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * width;
+    if (id < 0 || id >= vocab) {           // the host rejects such ids; never read out of range
+        for (int e = threadIdx.x; e < width; e += blockDim.x) o[e] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)id * width;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) o[e] = to_float(row[e]);
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// y = x * rsqrt(mean(x^2) + eps) * w, one block per row.  `rows` (optional)
+// picks which rows of x are normed: y[i] = norm(x[rows[i]]).
+template <typename TO, typename TW>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                               const int* __restrict__ rows, TO* __restrict__ y, int width, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) { const float v = xr[e]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TO* yr = y + (size_t)r * width;
+    for (int e = threadIdx.x; e < width; e += blockDim.x)
+        yr[e] = from_float<TO>(xr[e] * scale * to_float(w[e]));
+}
+
+// ------------------------------------------------- rotary + cache write
+// One block per (token, head) of the fused projection row
+// [q heads | k heads | v heads].  q is rotated in place; rotated k and raw v go
+// to the cache row of (slot, position): page page_table[slot][pos / page_size],
+// row pos % page_size of that page.
+template <typename T>
+__global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
+                                        const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                        const int* __restrict__ seq_slot,
+                                        const float* __restrict__ inv_freq,
+                                        T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                        const int* __restrict__ page_table, int max_pages, int page_size,
+                                        int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
+                                        int interleaved, int write_kv) {
+    const int t = blockIdx.x;
+    const int h = blockIdx.y;
+    const int pos = tok_pos[t];
+    T* src = qkv + (size_t)t * row_stride + (size_t)h * head_dim;
+    T* dst = src;
+    bool rotate = true;
+    if (h >= n_heads) {
+        if (!write_kv) return;
+        const int kvh = (h - n_heads) % n_kv_heads;
+        const bool is_v = (h - n_heads) >= n_kv_heads;
+        const int slot = seq_slot[tok_seq[t]];
+        T* cache = is_v ? v_cache : k_cache;
+        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+        dst = cache + (((size_t)page * page_size + (size_t)(pos % page_size)) * n_kv_heads + kvh) * head_dim;
+        rotate = !is_v;
+    }
+    const int half = rotary_dim / 2;
+    if (rotate) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const int d0 = interleaved ? 2 * i : i;
+            const int d1 = interleaved ? 2 * i + 1 : i + half;
+            const float a = (float)pos * inv_freq[i];
+            float s, c;
+            sincosf(a, &s, &c);
+            const float x0 = to_float(src[d0]), x1 = to_float(src[d1]);
+            dst[d0] = from_float<T>(x0 * c - x1 * s);
+            dst[d1] = from_float<T>(x0 * s + x1 * c);
+        }
+        if (dst != src)
+            for (int d = rotary_dim + threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = src[d];
+    } else {
+        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = src[d];
+    }
+}
+
+// y[i,:] = x[rows[i],:]
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows,
+                                   T* __restrict__ y, int width) {
+    const T* xr = x + (size_t)rows[blockIdx.x] * width;
+    T* yr = y + (size_t)blockIdx.x * width;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) yr[e] = xr[e];
+}
+
+}  // namespace mdma
+
+using namespace mdma;
+
+extern "C" {
+
+const char* mdma_last_error() { return error_buffer(); }
+
+int mdma_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
+                    int n_tokens, int width, int vocab, cudaStream_t stream) {
+    MDMA_REQUIRE(n_tokens >= 0 && width > 0 && vocab > 0, "embed_rows: bad sizes");
+    if (n_tokens == 0) return 0;
+    MDMA_DISPATCH_DTYPE(table_dtype, T,
+        embed_rows_kernel<T><<<n_tokens, 256, 0, stream>>>((const T*)table, ids, out, width, vocab));
+    MDMA_LAUNCH_OK("embed_rows");
+    return 0;
+}
+
+int mdma_rmsnorm(const float* x, const void* w, int w_dtype, const int* rows, void* y, int y_dtype,
+                 int n_rows, int width, float eps, cudaStream_t stream) {
+    MDMA_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes");
+    if (n_rows == 0) return 0;
+    const int threads = width >= 4096 ? 512 : 256;
+    MDMA_DISPATCH_DTYPE(y_dtype, TO,
+        MDMA_DISPATCH_DTYPE(w_dtype, TW,
+            rmsnorm_kernel<TO, TW><<<n_rows, threads, 0, stream>>>(x, (const TW*)w, rows, (TO*)y, width, eps)));
+    MDMA_LAUNCH_OK("rmsnorm");
+    return 0;
+}
+
+int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const int* tok_seq, const int* tok_pos,
+                          const int* seq_slot, const float* inv_freq, void* k_cache, void* v_cache,
+                          const int* page_table, int max_pages, int page_size,
+                          int n_tokens, int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
+                          int interleaved, int write_kv, cudaStream_t stream) {
+    MDMA_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads >= 0 && head_dim > 0, "rope_cache_write: bad sizes");
+    MDMA_REQUIRE(rotary_dim % 2 == 0 && rotary_dim <= head_dim, "rope_cache_write: rotary_dim %d does not fit head_dim %d", rotary_dim, head_dim);
+    MDMA_REQUIRE(!write_kv || (page_table && page_size > 0 && max_pages > 0), "rope_cache_write: no cache pages");
+    if (n_tokens == 0) return 0;
+    const int heads = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    dim3 grid(n_tokens, heads);
+    int threads = 32;
+    while (threads < head_dim / 2 && threads < 128) threads *= 2;
+    MDMA_DISPATCH_DTYPE(dtype, T,
+        rope_cache_write_kernel<T><<<grid, threads, 0, stream>>>(
+            (T*)qkv, row_stride, tok_seq, tok_pos, seq_slot, inv_freq, (T*)k_cache, (T*)v_cache,
+            page_table, max_pages, page_size, n_heads, n_kv_heads, head_dim, rotary_dim, interleaved, write_kv));
+    MDMA_LAUNCH_OK("rope_cache_write");
+    return 0;
+}
+
+int mdma_gather_rows(const void* x, int dtype, const int* rows, void* y, int n_rows, int width,
+                     cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    MDMA_DISPATCH_DTYPE(dtype, T,
+        gather_rows_kernel<T><<<n_rows, 256, 0, stream>>>((const T*)x, rows, (T*)y, width));
+    MDMA_LAUNCH_OK("gather_rows");
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,162 @@
+"""Python faces of the CUDA kernels.
+
+Each function checks what the kernel cannot check (devices, dtypes,
+contiguity, sizes), passes raw pointers and the current stream to the C entry
+point and raises `KernelError` with the library's message on failure.  There
+is no fallback: without the compiled library, or off the GPU, these raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+GEMM_STORE, GEMM_ACCUMULATE, GEMM_SWIGLU = 0, 1, 2
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _call(libname: str, fn: str, *args):
+    lib = _build.load(libname)
+    rc = getattr(lib, fn)(*args)
+    if rc != 0:
+        raise KernelError(lib.mdma_last_error().decode(errors="replace"))
+
+
+_i = ctypes.c_int
+_f = ctypes.c_float
+
+
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(table, ids, out)
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous()
+    n = ids.numel()
+    assert out.shape[0] >= n and out.shape[1] == table.shape[1] and out.is_contiguous()
+    _call("core", "mdma_embed_rows", _ptr(table), _i(dtype_code(table.dtype)), _ptr(ids), _ptr(out),
+          _i(n), _i(table.shape[1]), _i(table.shape[0]), _stream())
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
+    """out[i] = rmsnorm(x[rows[i]] or x[i]) * w; x is the float residual stream."""
+    _need_cuda(x, w, out, rows)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    width = x.shape[-1]
+    assert w.numel() == width and out.shape[-1] == width
+    n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
+    assert out.shape[0] >= n
+    if rows is not None:
+        assert rows.dtype == torch.int32
+    _call("core", "mdma_rmsnorm", _ptr(x), _ptr(w), _i(dtype_code(w.dtype)), _ptr(rows), _ptr(out),
+          _i(dtype_code(out.dtype)), _i(n), _i(width), _f(eps), _stream())
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = GEMM_STORE,
+              w2: Optional[torch.Tensor] = None, m: Optional[int] = None) -> None:
+    """out[:m] (=, +=) a[:m] @ w.T on the CUDA cores; SwiGLU mode takes gate=w, up=w2."""
+    _need_cuda(a, w, out, w2)
+    assert a.dim() == 2 and w.dim() == 2 and out.dim() == 2
+    assert a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
+    M = a.shape[0] if m is None else m
+    N, K = w.shape
+    assert a.shape[1] == K and out.shape[1] == N and out.shape[0] >= M and a.shape[0] >= M
+    if w2 is not None:
+        assert w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous()
+    _call("core", "mdma_gemm_simt", _i(mode), _ptr(a), _i(dtype_code(a.dtype)), _i(a.stride(0)),
+          _ptr(w), _ptr(w2), _i(dtype_code(w.dtype)), _ptr(out), _i(dtype_code(out.dtype)),
+          _i(out.stride(0)), _i(M), _i(N), _i(K), _stream())
+
+
+def rope_cache_write(qkv: torch.Tensor, n_tokens: int, tok_seq, tok_pos, seq_slot, inv_freq,
+                     k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                     page_table: Optional[torch.Tensor], max_pages: int, page_size: int,
+                     n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+                     interleaved: bool, write_kv: bool) -> None:
+    _need_cuda(qkv, tok_seq, tok_pos, seq_slot, inv_freq, k_cache, v_cache, page_table)
+    assert qkv.stride(1) == 1 and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2
+    if write_kv:
+        assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+        assert k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+    _call("core", "mdma_rope_cache_write", _ptr(qkv), _i(dtype_code(qkv.dtype)), _i(qkv.stride(0)),
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(inv_freq), _ptr(k_cache), _ptr(v_cache),
+          _ptr(page_table), _i(max_pages), _i(page_size),
+          _i(n_tokens), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(rotary_dim), _i(int(interleaved)),
+          _i(int(write_kv)), _stream())
+
+
+def attention_simple(q: torch.Tensor, n_tokens: int, k_cache, v_cache, tok_seq, tok_pos, seq_slot,
+                     page_table: torch.Tensor, max_pages: int, page_size: int,
+                     out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                     window: int, scale: float) -> None:
+    """q: rows of the fused projection (first n_heads*head_dim columns are the queries)."""
+    _need_cuda(q, k_cache, v_cache, tok_seq, tok_pos, seq_slot, out, page_table)
+    assert q.stride(1) == 1 and out.is_contiguous() and out.dtype == q.dtype == k_cache.dtype
+    assert out.shape[1] == n_heads * head_dim and out.shape[0] >= n_tokens
+    _call("core", "mdma_attention_simple", _ptr(q), _i(dtype_code(q.dtype)), _i(q.stride(0)),
+          _ptr(k_cache), _ptr(v_cache), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot),
+          _ptr(page_table), _i(max_pages), _i(page_size), _ptr(out),
+          _i(n_tokens), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window),
+          _f(scale), _stream())
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(x, rows, out)
+    assert x.is_contiguous() and out.is_contiguous() and rows.dtype == torch.int32
+    _call("core", "mdma_gather_rows", _ptr(x), _i(dtype_code(x.dtype)), _ptr(rows), _ptr(out),
+          _i(rows.numel()), _i(x.shape[1]), _stream())
+
+
+def argmax(logits: torch.Tensor, tokens: torch.Tensor, flags: Optional[torch.Tensor] = None,
+           n_rows: Optional[int] = None) -> None:
+    _need_cuda(logits, tokens, flags)
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and tokens.dtype == torch.int32
+    n = logits.shape[0] if n_rows is None else n_rows
+    _call("core", "mdma_argmax", _ptr(logits), _i(n), _i(logits.shape[1]), _ptr(tokens), _ptr(flags),
+          _stream())
+
+
+def sample(logits: torch.Tensor, uniforms: torch.Tensor, tokens: torch.Tensor, probs_scratch: torch.Tensor,
+           temperature: float, top_p: float, min_p: float, penalty: float, penalty_window: int,
+           history: Optional[torch.Tensor] = None, history_len: Optional[torch.Tensor] = None,
+           flags: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
+    _need_cuda(logits, uniforms, tokens, probs_scratch, history, history_len, flags)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    assert uniforms.dtype == torch.float32 and tokens.dtype == torch.int32
+    n = logits.shape[0] if n_rows is None else n_rows
+    assert probs_scratch.dtype == torch.float32 and probs_scratch.numel() >= n * logits.shape[1]
+    hstride = 0
+    if history is not None:
+        assert history.dtype == torch.int32 and history_len.dtype == torch.int32 and history.is_contiguous()
+        hstride = history.shape[1]
+    _call("core", "mdma_sample", _ptr(logits), _i(n), _i(logits.shape[1]), _ptr(history),
+          _ptr(history_len), _i(hstride), _ptr(uniforms), _f(temperature), _f(top_p), _f(min_p),
+          _f(penalty), _i(penalty_window), _ptr(probs_scratch), _ptr(tokens), _ptr(flags), _stream())

@@ -1,0 +1,94 @@
+"""Grouped-query causal attention over the cache.
+
+q, k, v = h Wq^T, h Wk^T, h Wv^T (no biases); q and k take the position
+encoding, k and v go to the cache; a query at position p reads the keys
+[first, p] of its own sequence (first = 0, or p+1-window), kv head = q head //
+(heads / kv heads), scores (q.k) * scale through a float softmax; the result
+times Wo^T is added to the residual stream (src/model/arch/llama.rs:195-212,
+src/backend/cpu.rs:530-590).  Heads, groups, head size, scale and window are
+parameters.  A site that reads another site's cache has no k/v matrices and
+writes nothing.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache import KVNeed
+from ..registry import MIXERS, POSITIONS
+from ..spec import TensorSpec
+from .base import Part
+from .linear import Linear
+
+
+@MIXERS.register("attention")
+class Attention(Part):
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["num_heads"])
+        self.n_kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.scale = float(p["scale"])
+        self.window = int(p.get("window", 0) or 0)
+        self.shared_cache = bool(p.get("shared_cache", False))
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_heads} heads do not divide over {self.n_kv_heads} kv heads")
+        pos = p["position"]
+        self.position = POSITIONS.get(pos.kind)(pos)
+        self.q_width = self.n_heads * self.head_dim
+        self.kv_width = self.n_kv_heads * self.head_dim
+        self.row_width = self.q_width + (0 if self.shared_cache else 2 * self.kv_width)
+
+    def children(self):
+        return [self.position]
+
+    def tensor_specs(self):
+        specs = {"q_proj.weight": TensorSpec((self.q_width, self.hidden))}
+        if not self.shared_cache:
+            specs["k_proj.weight"] = TensorSpec((self.kv_width, self.hidden))
+            specs["v_proj.weight"] = TensorSpec((self.kv_width, self.hidden))
+        specs["o_proj.weight"] = TensorSpec((self.hidden, self.q_width))
+        return specs
+
+    def kv_need(self):
+        return KVNeed(self.n_kv_heads, self.head_dim, self.window)
+
+    def state_need(self):
+        return None
+
+    def workspace(self):
+        return {"qkv": (self.row_width, "act"), "attn_out": (self.q_width, "act")}
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.position.bind({}, rt)
+        if self.shared_cache:
+            fused = tensors["q_proj.weight"]
+        else:
+            # one product for q, k and v: rows [q heads | k heads | v heads]
+            fused = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
+                               tensors["v_proj.weight"]], dim=0).contiguous()
+        self.qkv_proj = Linear(fused, rt)
+        self.o_proj = Linear(tensors["o_proj.weight"], rt)
+
+    def forward(self, ctx, h, x, view, owns_cache=True):
+        n = ctx.n_tokens
+        qkv = ctx.buf("qkv", self.row_width)
+        out = ctx.buf("attn_out", self.q_width)
+        self.qkv_proj.store(h, qkv, n)
+        write = owns_cache and not self.shared_cache
+        self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, view, write)
+        if self.rt.attention == "fast":
+            from .. import ops_tensor
+            ops_tensor.attention(ctx, qkv, view, out, self.n_heads, self.n_kv_heads, self.head_dim,
+                                 self.window, self.scale)
+        else:
+            ops.attention_simple(qkv, n, view.k, view.v, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
+                                 view.page_table, view.max_pages, view.page_size, out,
+                                 self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
+        self.o_proj.accumulate(out, x, n)
+
+    def resident_bytes(self):
+        return self.qkv_proj.bytes() + self.o_proj.bytes()

@@ -1,0 +1,42 @@
+"""Matrix products of the parts: y = a @ W.T, with the three endings the
+model needs (store, add into the float residual stream, SwiGLU of two
+products).  Chooses the tensor-core kernel when the runtime asks for it and
+the shape allows, else the CUDA-core kernel; both are this library's own."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from .base import Runtime
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, rt: Runtime, weight2: Optional[torch.Tensor] = None):
+        self.w, self.w2, self.rt = weight, weight2, rt
+        self.out_features, self.in_features = weight.shape
+        self._tensor_ok = False
+        if rt.gemm == "tensor" and weight.dtype == torch.bfloat16:
+            from .. import ops_tensor
+            self._tensor_ok = ops_tensor.gemm_supported(self.out_features, self.in_features)
+
+    def _run(self, mode: int, a: torch.Tensor, out: torch.Tensor, m: int) -> None:
+        if self._tensor_ok:
+            from .. import ops_tensor
+            ops_tensor.gemm(a, self.w, out, mode, self.w2, m)
+        else:
+            ops.gemm_simt(a, self.w, out, mode, self.w2, m)
+
+    def store(self, a, out, m):
+        self._run(ops.GEMM_STORE, a, out, m)
+
+    def accumulate(self, a, x, m):
+        self._run(ops.GEMM_ACCUMULATE, a, x, m)
+
+    def swiglu(self, a, out, m):
+        self._run(ops.GEMM_SWIGLU, a, out, m)
+
+    def bytes(self) -> int:
+        n = self.w.numel() * self.w.element_size()
+        return n * (2 if self.w2 is not None else 1)
