@@ -212,8 +212,9 @@ class SequenceCache:
             for g in self.groups:
                 g.trim(slot, self.lengths[slot])
 
-    def view(self, site: int) -> KVView:
-        state = self.states.get(site)
+    def view(self, site: int, state_site: Optional[int] = None) -> KVView:
+        """Pages of `site`; the fixed-size state of `state_site` (default: the same site)."""
+        state = self.states.get(site if state_site is None else state_site)
         if site not in self.site_group:
             return KVView(None, None, None, self.page_size, self.max_pages, 0, state)
         gi, j = self.site_group[site]

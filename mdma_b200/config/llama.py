@@ -135,7 +135,9 @@ class LlamaConfig:
             if not isinstance(scaling, dict):
                 raise ConfigError("rope_scaling must be an object or null")
             kind = scaling.get("rope_type", scaling.get("type"))
-            if kind not in (None, "default"):
+            if kind not in (None, "default", "llama3"):
+                raise ConfigError(f"rope_scaling.rope_type {kind!r} is not implemented (only 'llama3')")
+            if kind == "llama3":
                 known = {"rope_type", "type", "factor", "low_freq_factor", "high_freq_factor",
                          "original_max_position_embeddings"}
                 extra = sorted(set(scaling) - known)

@@ -1,0 +1,370 @@
+// bfloat16 matrix products on the fifth-generation tensor cores.
+//
+//   out[t, f] (=, +=)  sum_k  X[t, k] * W[f, k]        X: tokens x K, W: features x K
+//
+// The weight matrix is the 128-row MMA operand (A) and the tokens are the MMA's
+// N dimension, so that one kernel serves a prefill of thousands of tokens
+// (N tile 256) and a decode step of a handful (N tile 16) while every tile
+// still streams 128 weight rows.  Per block: one warp issues TMA loads of
+// 128 x 64 weight boxes and N x 64 activation boxes (128-byte swizzle) into a
+// ring of shared-memory stages, one thread issues tcgen05.mma into a float
+// accumulator in tensor memory, four warps read the accumulator back
+// (tcgen05.ld; lane = feature, column = token) and apply the ending:
+//   store (bf16 or float), add into the float residual stream, SwiGLU of two
+//   accumulators (gate and up share the activation tile), or float partial
+//   sums of a K split, reduced afterwards in split order.
+// Sizes: any token count, any feature count, K a multiple of 8 (16-byte rows
+// for TMA); tails are zero-filled by TMA and masked at the store.
+#include <unordered_map>
+#include <mutex>
+#include <string.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace mdma {
+
+enum TcMode : int { kTcStore = 0, kTcAccumulate = 1, kTcSwiGLU = 2, kTcPartial = 3 };
+
+constexpr int kBM = 128;        // features per tile (MMA M)
+constexpr int kBK = 64;         // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kTcThreads = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+
+struct TcParams {
+    void* out; int ldo; int out_f32;
+    int n_tokens, n_features, k_blocks, kb_per_split;
+    float* partial;            // [splits, n_tokens, n_features] when MODE == kTcPartial
+    int* status;               // device word set non-zero when a wait ran out
+};
+
+template <int BN, int MODE>
+struct TcSmem {
+    static constexpr int kA = kBM * kBK * 2;
+    static constexpr int kB = BN * kBK * 2;
+    static constexpr int kStage = kA * (MODE == kTcSwiGLU ? 2 : 1) + (kB < 1024 ? 1024 : kB);
+    // small token tiles leave room for two blocks per SM (decode: more blocks than SMs stay balanced)
+    static constexpr int kBudget = (BN <= 64 ? 110 : 200) * 1024;
+    static constexpr int kStages = (kBudget / kStage) < 8 ? (kBudget / kStage) : 8;
+    static constexpr int kBytes = kStages * kStage + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int kTmemCols = (MODE == kTcSwiGLU ? 2 : 1) * BN < 32 ? 32 : (MODE == kTcSwiGLU ? 2 : 1) * BN;
+};
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+               const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    using S = TcSmem<BN, MODE>;
+    constexpr int kStages = S::kStages;
+    constexpr bool kDual = MODE == kTcSwiGLU;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - ptx::smem_addr(smem_raw));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + kStages * S::kStage);
+    const uint32_t bar0 = base + kStages * S::kStage;
+    // barrier layout: full[kStages], empty[kStages], acc_full, then the TMEM base word and abort flag
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+    const uint32_t acc_bar = bar0 + 8u * (2 * kStages);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f0 = blockIdx.x * kBM;
+    const int t0 = blockIdx.y * BN;
+    const int kb_begin = blockIdx.z * p.kb_per_split;
+    const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+    const int n_kb = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+        ptx::mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_addr((const void*)tmem_slot), S::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: TMA loads into the ring -------------------------------
+        ptx::prefetch_tensormap(&map_w);
+        ptx::prefetch_tensormap(&map_x);
+        if (kDual) ptx::prefetch_tensormap(&map_w2);
+        int issued = 0;
+        for (int i = 0; i < n_kb; ++i) {
+            const int s = i % kStages;
+            if (!ptx::mbar_wait(empty_bar(s), ((i / kStages) & 1) ^ 1, abort_flag)) break;
+            const uint32_t stage = base + s * S::kStage;
+            ptx::mbar_expect_tx(full_bar(s), S::kA * (kDual ? 2 : 1) + S::kB);
+            const int k = (kb_begin + i) * kBK;
+            ptx::tma_load_2d(stage, &map_w, full_bar(s), k, f0);
+            if (kDual) ptx::tma_load_2d(stage + S::kA, &map_w2, full_bar(s), k, f0);
+            ptx::tma_load_2d(stage + S::kA * (kDual ? 2 : 1), &map_x, full_bar(s), k, t0);
+            ++issued;
+        }
+        if (*abort_flag) {
+            // let the copies in flight land before the block's shared memory is given up
+            for (int i = max(0, issued - kStages); i < issued; ++i)
+                ptx::mbar_wait(full_bar(i % kStages), (i / kStages) & 1, abort_flag);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer -------------------------------------------------------
+        constexpr uint32_t idesc = ptx::idesc_bf16_f32(kBM, BN);
+        bool ok = true;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            const int s = i % kStages;
+            ok = ptx::mbar_wait(full_bar(s), (i / kStages) & 1, abort_flag);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t stage = base + s * S::kStage;
+            const uint32_t a_addr = stage, b_addr = stage + S::kA * (kDual ? 2 : 1);
+#pragma unroll
+            for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+                const uint64_t b_desc = ptx::smem_desc_sw128(b_addr + kk * kUmmaK * 2);
+                const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+                ptx::mma_bf16_ss(tmem_base, ptx::smem_desc_sw128(a_addr + kk * kUmmaK * 2), b_desc, idesc, acc);
+                if (kDual)
+                    ptx::mma_bf16_ss(tmem_base + BN, ptx::smem_desc_sw128(a_addr + S::kA + kk * kUmmaK * 2),
+                                     b_desc, idesc, acc);
+            }
+            ptx::mma_commit(empty_bar(s));      // the stage is free once these MMAs have read it
+        }
+        ptx::mma_commit(acc_bar);               // the accumulator is complete
+    } else if (warp >= 2) {
+        // ---- epilogue: TMEM -> registers -> global ----------------------------
+        const int quad = warp & 3;              // the TMEM lanes this warp may read
+        const int f = f0 + quad * 32 + lane;
+        const bool ok = ptx::mbar_wait(acc_bar, 0, abort_flag);
+        ptx::tc_fence_after_sync();
+        if (ok && n_kb > 0) {
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (t0 + c >= p.n_tokens) break;           // uniform over the warp
+                float v[16], u[16];
+                ptx::tmem_load_16(lane_addr + c, v);
+                if (kDual) ptx::tmem_load_16(lane_addr + BN + c, u);
+                if (f < p.n_features) {
+                    const int valid = min(16, p.n_tokens - (t0 + c));
+                    if (MODE == kTcAccumulate) {
+                        // read the 16 residual values first so the loads overlap, then add and store
+                        float* o = reinterpret_cast<float*>(p.out) + (size_t)(t0 + c) * p.ldo + f;
+                        float old[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) old[j] = j < valid ? o[(size_t)j * p.ldo] : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (j < valid) o[(size_t)j * p.ldo] = old[j] + v[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (j >= valid) break;
+                            const int t = t0 + c + j;
+                            float r = v[j];
+                            if (MODE == kTcSwiGLU) r = r / (1.0f + __expf(-r)) * u[j];
+                            if (MODE == kTcPartial) {
+                                p.partial[((size_t)blockIdx.z * p.n_tokens + t) * p.n_features + f] = r;
+                            } else if (p.out_f32) {
+                                reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + f] = r;
+                            } else {
+                                reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(r);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, S::kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+// out (=, +=) sum over splits of partial, in split order.
+template <int MODE>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int n_tokens, int n_features,
+                                     void* __restrict__ out, int ldo, int out_f32) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)n_tokens * n_features;
+    if (i >= total) return;
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * total + i];
+    const size_t t = i / n_features, f = i % n_features;
+    if (MODE == kTcAccumulate) reinterpret_cast<float*>(out)[t * ldo + f] += acc;
+    else if (out_f32) reinterpret_cast<float*>(out)[t * ldo + f] = acc;
+    else reinterpret_cast<__nv_bfloat16*>(out)[t * ldo + f] = __float2bfloat16_rn(acc);
+}
+
+// ---- tensor maps ----------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; uint64_t rows, cols, pitch; uint32_t box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ k.rows; h = h * 1000003u ^ k.cols; h = h * 1000003u ^ k.pitch; h = h * 1000003u ^ k.box_rows;
+        return h;
+    }
+};
+
+// A bf16 matrix [rows, cols] with `pitch` bytes per row, tiled in boxes of box_rows x 64.
+static int make_map_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t pitch,
+                       uint32_t box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    const MapKey key{ptr, rows, cols, pitch, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail("gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("gemm_tc: cuTensorMapEncodeTiled failed with %d (ptr %p rows %llu cols %llu pitch %llu)",
+                                       (int)r, ptr, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)pitch);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+}  // namespace mdma
+
+using namespace mdma;
+
+template <int BN, int MODE>
+static int run_tc(const void* x, int ldx, const void* w, const void* w2, int K, TcParams p, int splits,
+                  cudaStream_t stream) {
+    using S = TcSmem<BN, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+        if (e != cudaSuccess) return fail("gemm_tc: cannot reserve %d bytes of shared memory: %s", S::kBytes, cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap mw, mw2, mx;
+    if (int rc = make_map_2d(&mw, w, (uint64_t)p.n_features, (uint64_t)K, (uint64_t)K * 2, kBM)) return rc;
+    mw2 = mw;
+    if (MODE == kTcSwiGLU)
+        if (int rc = make_map_2d(&mw2, w2, (uint64_t)p.n_features, (uint64_t)K, (uint64_t)K * 2, kBM)) return rc;
+    if (int rc = make_map_2d(&mx, x, (uint64_t)p.n_tokens, (uint64_t)K, (uint64_t)ldx * 2, BN)) return rc;
+    dim3 grid((p.n_features + kBM - 1) / kBM, (p.n_tokens + BN - 1) / BN, splits);
+    gemm_tc_kernel<BN, MODE><<<grid, kTcThreads, S::kBytes, stream>>>(mw, mw2, mx, p);
+    MDMA_LAUNCH_OK("gemm_tc");
+    return 0;
+}
+
+template <int MODE>
+static int run_tc_bn(int bn, const void* x, int ldx, const void* w, const void* w2, int K, const TcParams& p,
+                     int splits, cudaStream_t stream) {
+    switch (bn) {
+        case 16: return run_tc<16, MODE>(x, ldx, w, w2, K, p, splits, stream);
+        case 32: return run_tc<32, MODE>(x, ldx, w, w2, K, p, splits, stream);
+        case 64: return run_tc<64, MODE>(x, ldx, w, w2, K, p, splits, stream);
+        case 128: return run_tc<128, MODE>(x, ldx, w, w2, K, p, splits, stream);
+        case 256: return run_tc<256, MODE>(x, ldx, w, w2, K, p, splits, stream);
+    }
+    return fail("gemm_tc: no token tile of %d", bn);
+}
+
+extern "C" {
+
+const char* mdma_last_error() { return error_buffer(); }
+
+// Returns 1 if the tensor-core kernel takes this weight shape.
+int mdma_gemm_tc_supported(int n_features, int K) { return (K % 8 == 0 && K >= 8 && n_features >= 1) ? 1 : 0; }
+
+// Bytes of float scratch a call with these sizes needs (0 when it does not split K).
+// `splits` <= 0 asks the library to choose.
+int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_count, int* bn_out, int* splits_out) {
+    int bn = 16;
+    while (bn < 256 && bn < n_tokens) bn *= 2;
+    const int k_blocks = (K + kBK - 1) / kBK;
+    const long tiles = (long)((n_features + kBM - 1) / kBM) * ((n_tokens + bn - 1) / bn);
+    int splits = 1;
+    if (mode != kTcSwiGLU && tiles < sm_count) {
+        splits = (int)((sm_count + tiles - 1) / tiles);
+        if (splits > 16) splits = 16;
+        if (splits > k_blocks / 4) splits = k_blocks / 4 > 0 ? k_blocks / 4 : 1;
+    }
+    *bn_out = bn;
+    *splits_out = splits;
+    return 0;
+}
+
+int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2, void* out, int out_f32,
+                 int ldo, int n_tokens, int n_features, int K, int bn, int splits, float* scratch,
+                 long scratch_floats, int* status, cudaStream_t stream) {
+    MDMA_REQUIRE(n_tokens >= 0 && n_features > 0 && K > 0, "gemm_tc: bad sizes");
+    MDMA_REQUIRE(K % 8 == 0, "gemm_tc: K=%d is not a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
+    MDMA_REQUIRE(ldx % 8 == 0 && ldx >= K, "gemm_tc: activation pitch %d must be a multiple of 8 and at least K", ldx);
+    MDMA_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && (!w2 || ((uintptr_t)w2 & 15) == 0),
+                 "gemm_tc: operands must be 16-byte aligned");
+    MDMA_REQUIRE(mode != kTcSwiGLU || w2, "gemm_tc: SwiGLU needs two weights");
+    MDMA_REQUIRE(mode != kTcAccumulate || out_f32, "gemm_tc: the residual stream is float");
+    MDMA_REQUIRE(mode >= 0 && mode <= 2, "gemm_tc: unknown mode %d", mode);
+    MDMA_REQUIRE((n_tokens + bn - 1) / bn <= 65535, "gemm_tc: too many token tiles");
+    if (n_tokens == 0) return 0;
+    const int k_blocks = (K + kBK - 1) / kBK;
+    if (splits < 1) splits = 1;
+    if (splits > k_blocks) splits = k_blocks;
+    if (mode == kTcSwiGLU) splits = 1;
+    TcParams p;
+    p.out = out; p.ldo = ldo; p.out_f32 = out_f32;
+    p.n_tokens = n_tokens; p.n_features = n_features; p.k_blocks = k_blocks;
+    p.kb_per_split = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + p.kb_per_split - 1) / p.kb_per_split;     // no empty split
+    p.partial = nullptr; p.status = status;
+    if (splits == 1) {
+        if (mode == kTcStore) return run_tc_bn<kTcStore>(bn, x, ldx, w, w2, K, p, 1, stream);
+        if (mode == kTcAccumulate) return run_tc_bn<kTcAccumulate>(bn, x, ldx, w, w2, K, p, 1, stream);
+        return run_tc_bn<kTcSwiGLU>(bn, x, ldx, w, w2, K, p, 1, stream);
+    }
+    const long need = (long)splits * n_tokens * n_features;
+    MDMA_REQUIRE(scratch && scratch_floats >= need, "gemm_tc: a %d-way K split needs %ld floats of scratch, %ld given", splits, need, scratch_floats);
+    p.partial = scratch;
+    if (int rc = run_tc_bn<kTcPartial>(bn, x, ldx, w, w2, K, p, splits, stream)) return rc;
+    const size_t total = (size_t)n_tokens * n_features;
+    const int blocks = (int)((total + 255) / 256);
+    if (mode == kTcAccumulate)
+        splitk_reduce_kernel<kTcAccumulate><<<blocks, 256, 0, stream>>>(scratch, splits, n_tokens, n_features, out, ldo, out_f32);
+    else
+        splitk_reduce_kernel<kTcStore><<<blocks, 256, 0, stream>>>(scratch, splits, n_tokens, n_features, out, ldo, out_f32);
+    MDMA_LAUNCH_OK("splitk_reduce");
+    return 0;
+}
+
+}  // extern "C"

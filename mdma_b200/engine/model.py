@@ -97,7 +97,8 @@ class DecoderModel:
         self.embedding.forward(ctx, ctx.ids, x)
         for n, entry in enumerate(self.spec.schedule):
             site = n if entry.cache is None else entry.cache
-            self.blocks[entry.layer].forward(ctx, x, cache.view(site), owns_cache=entry.cache is None)
+            self.blocks[entry.layer].forward(ctx, x, cache.view(site, state_site=n),
+                                             owns_cache=entry.cache is None)
         if ctx.n_want:
             h = ctx.buf("h_rows", self.spec.hidden_size)
             self.final_norm.forward(ctx, x, h, rows=ctx.want_rows, n_rows=ctx.n_want)

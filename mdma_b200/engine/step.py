@@ -73,11 +73,41 @@ class StepContext:
         return t
 
 
+def memory_plan(model: DecoderModel, expected, dtype, max_tokens, max_slots, max_context, page_size,
+                chunk_tokens) -> dict:
+    """Bytes the engine will hold, from sizes alone (src/model/planning.rs:55-125)."""
+    elem = 4 if dtype == torch.float32 else 2
+    weights = 0
+    for name, ts in expected.items():
+        n = int(np.prod(ts.shape))
+        weights += n * (4 if (ts.kind == "int" or dtype == torch.float32) else (2 if ts.kind == "matrix" else 4))
+    cache = SequenceCache(model.kv_needs(), model.state_needs(), max_tokens, max_slots, max_context, dtype,
+                          "meta", page_size, allocate=False)
+    ws = sum(chunk_tokens * cols * (4 if kind == "f32" else elem)
+             for cols, kind in model.workspace_columns().values())
+    return {"weights_bytes": weights, "cache_bytes": cache.bytes, "workspace_bytes": ws,
+            "total_bytes": weights + cache.bytes + ws, "cache_pages": cache.n_pages,
+            "page_size": page_size, "slots": max_slots, "chunk_tokens": chunk_tokens}
+
+
+def plan_only(model_dir: str, dtype="bfloat16", max_batch: int = 1, max_context: Optional[int] = None,
+              chunk_tokens: int = 8192, page_size: int = 64) -> dict:
+    """The memory plan of a model folder without touching a device or reading weights."""
+    arch, config = load_config(model_dir)
+    spec = arch.describe(config)
+    model = DecoderModel(spec)
+    ctx = int(max_context or spec.max_positions)
+    max_tokens = max_batch * (-(-ctx // page_size)) * page_size
+    return memory_plan(model, model.expected_tensors(), _DTYPES[dtype], max_tokens, max_batch, ctx,
+                       page_size, max(1, min(chunk_tokens, max_tokens)))
+
+
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, *, config: Optional[dict] = None,
                  seed: Optional[int] = None, dtype="bfloat16", max_tokens: Optional[int] = None,
                  max_batch: int = 8, max_context: Optional[int] = None, chunk_tokens: int = 8192,
-                 device="cuda:0", reserve_mib: int = 256, kernels: str = "auto", page_size: int = 64):
+                 device="cuda:0", reserve_mib: int = 256, kernels: str = "auto", page_size: int = 64,
+                 vram_bytes: Optional[int] = None, context_hint: Optional[int] = None):
         if dtype not in _DTYPES:
             raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
         self.dtype = _DTYPES[dtype]
@@ -94,6 +124,9 @@ class Engine:
         self.vocab_size = self.spec.vocab_size
 
         self.max_context = int(max_context or self.spec.max_positions)
+        if max_context is None and context_hint is not None:
+            # a caller that knows its longest sequence need not pay for the model's full context
+            self.max_context = max(1, min(self.max_context, int(context_hint)))
         self.page_size = page_size
         pages_per_seq = -(-self.max_context // page_size)
         if max_tokens is None:
@@ -118,6 +151,8 @@ class Engine:
         expected = self.model.expected_tensors()
         self.plan = self._plan(expected)
         free, _total = torch.cuda.mem_get_info(self.device)
+        if vram_bytes is not None:
+            free = min(free, int(vram_bytes))
         need = self.plan["total_bytes"] + reserve_mib * (1 << 20)
         if need > free:
             raise MemoryBudgetError(need, free, self.plan)
@@ -153,21 +188,8 @@ class Engine:
 
     # ---- planning ----------------------------------------------------------
     def _plan(self, expected) -> dict:
-        elem = 4 if self.dtype == torch.float32 else 2
-        weights = 0
-        for name, ts in expected.items():
-            n = int(np.prod(ts.shape))
-            weights += n * (4 if (ts.kind == "int" or self.dtype == torch.float32) else
-                            (2 if ts.kind == "matrix" else 4))
-        cache = SequenceCache(self.model.kv_needs(), self.model.state_needs(), self.max_tokens,
-                              self.max_slots, self.max_context, self.dtype, "meta", self.page_size,
-                              allocate=False)
-        ws = 0
-        for name, (cols, kind) in self.model.workspace_columns().items():
-            ws += self.chunk_tokens * cols * (4 if kind == "f32" else elem)
-        return {"weights_bytes": weights, "cache_bytes": cache.bytes, "workspace_bytes": ws,
-                "total_bytes": weights + cache.bytes + ws, "cache_pages": cache.n_pages,
-                "page_size": self.page_size, "slots": self.max_slots, "chunk_tokens": self.chunk_tokens}
+        return memory_plan(self.model, expected, self.dtype, self.max_tokens, self.max_slots,
+                           self.max_context, self.page_size, self.chunk_tokens)
 
     # ---- sequences ---------------------------------------------------------
     def acquire(self) -> int:
@@ -175,6 +197,17 @@ class Engine:
 
     def release(self, slot: int) -> None:
         self.cache.release(slot)
+
+    @property
+    def max_slots_free(self) -> int:
+        return self.cache.slots.free_count
+
+    def fits(self, sizes) -> bool:
+        """Whether sequences of (prompt length, token budget) can be live together in an empty cache."""
+        if len(sizes) > self.max_slots:
+            return False
+        pages = sum(-(-(p + b - 1) // self.page_size) for p, b in sizes)
+        return pages <= self.cache.n_pages and all(p + b - 1 <= self.max_context for p, b in sizes)
 
     # ---- the step ----------------------------------------------------------
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -279,6 +312,7 @@ class Engine:
         ctx.max_new, ctx.max_len = max_new, max_len
         ctx.host_seq_new = [take for _, _, take in pieces]
         ctx.host_seq_pos0 = list(seq_pos0)
+        ctx.host_seq_slot = list(seq_slot)
         contiguous = dest_rows == list(range(dest_rows[0], dest_rows[0] + W)) if W else True
         if W and contiguous:
             out = logits[dest_rows[0]:dest_rows[0] + W]

@@ -1,0 +1,80 @@
+"""Python faces of the tensor-core kernels (bfloat16 only): the tcgen05 matrix
+product and the fast attention kernels.  As in `ops`, nothing here falls back:
+a shape the kernels refuse raises `KernelError`."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import ops
+from .csrc import build as _build
+from .ops import KernelError, _call, _f, _i, _need_cuda, _ptr, _stream
+
+_state: dict = {}
+
+
+def _device_state(device: torch.device) -> dict:
+    st = _state.get(device.index)
+    if st is None:
+        st = {"status": torch.zeros(4, dtype=torch.int32, device=device),
+              "scratch": torch.empty(1 << 20, dtype=torch.float32, device=device),
+              "sms": torch.cuda.get_device_properties(device).multi_processor_count}
+        _state[device.index] = st
+    return st
+
+
+def check_status(device: torch.device) -> None:
+    """Raise if a tensor-core kernel gave up on a wait since the last check (synchronises)."""
+    st = _state.get(device.index)
+    if st is not None and int(st["status"][0].item()) != 0:
+        st["status"].zero_()
+        raise KernelError("a tensor-core kernel ran into its wait limit; its output is not valid")
+
+
+def gemm_supported(n_features: int, k: int) -> bool:
+    return k % 8 == 0 and k >= 8
+
+
+def gemm_plan(mode: int, n_tokens: int, n_features: int, k: int, sms: int) -> tuple[int, int]:
+    lib = _build.load("tensor")
+    bn, splits = ctypes.c_int(0), ctypes.c_int(0)
+    lib.mdma_gemm_tc_plan(_i(mode), _i(n_tokens), _i(n_features), _i(k), _i(sms),
+                          ctypes.byref(bn), ctypes.byref(splits))
+    return bn.value, splits.value
+
+
+def reserve_scratch(device: torch.device, floats: int) -> None:
+    """Make the split-K scratch at least this large (call outside graph capture)."""
+    st = _device_state(device)
+    if st["scratch"].numel() < floats:
+        st["scratch"] = torch.empty(floats, dtype=torch.float32, device=device)
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GEMM_STORE,
+         w2: Optional[torch.Tensor] = None, m: Optional[int] = None,
+         bn: Optional[int] = None, splits: Optional[int] = None) -> None:
+    """out[:m] (=, +=) a[:m] @ w.T on the tensor cores; SwiGLU mode takes gate=w, up=w2."""
+    _need_cuda(a, w, out, w2)
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core product takes bfloat16 operands")
+    assert a.dim() == 2 and w.dim() == 2 and a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
+    M = a.shape[0] if m is None else m
+    N, K = w.shape
+    assert a.shape[1] == K and out.shape[1] == N and out.shape[0] >= M and a.shape[0] >= M
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError(f"output dtype {out.dtype} is not supported")
+    st = _device_state(a.device)
+    if bn is None or splits is None:
+        pbn, psplits = gemm_plan(mode, M, N, K, st["sms"])
+        bn = bn or pbn
+        splits = splits or psplits
+    need = splits * M * N if splits > 1 else 0
+    if need > st["scratch"].numel():
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("split-K scratch is too small and cannot grow during graph capture")
+        reserve_scratch(a.device, need)
+    _call("tensor", "mdma_gemm_tc", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), _ptr(out),
+          _i(int(out.dtype == torch.float32)), _i(out.stride(0)), _i(M), _i(N), _i(K), _i(bn), _i(splits),
+          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]), _stream())

@@ -21,6 +21,11 @@ from .base import Part
 from .linear import Linear
 
 
+def ops_tensor_attention_ready() -> bool:
+    from .. import ops_tensor
+    return hasattr(ops_tensor, "attention")
+
+
 @MIXERS.register("attention")
 class Attention(Part):
     def __init__(self, spec):
@@ -80,7 +85,7 @@ class Attention(Part):
         self.qkv_proj.store(h, qkv, n)
         write = owns_cache and not self.shared_cache
         self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, view, write)
-        if self.rt.attention == "fast":
+        if self.rt.attention == "fast" and ops_tensor_attention_ready():
             from .. import ops_tensor
             ops_tensor.attention(ctx, qkv, view, out, self.n_heads, self.n_kv_heads, self.head_dim,
                                  self.window, self.scale)

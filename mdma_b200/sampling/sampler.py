@@ -1,0 +1,62 @@
+"""Token selection on the device for a batch of logits rows."""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from .params import SamplingParams, uniform
+
+
+class DeviceSampler:
+    """Owns the small device buffers the sampling kernels need for up to
+    `max_rows` rows; `sample` returns host lists (tokens, non-finite flags)."""
+
+    def __init__(self, vocab_size: int, max_rows: int, device, history_cap: int = 64):
+        self.vocab, self.max_rows, self.device = vocab_size, max_rows, device
+        self.tokens = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.flags = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.uniforms = torch.zeros(max_rows, dtype=torch.float32, device=device)
+        self.history_cap = max(1, history_cap)
+        self.history = torch.zeros((max_rows, self.history_cap), dtype=torch.int32, device=device)
+        self.history_len = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self._probs: Optional[torch.Tensor] = None
+        self._out_host = torch.empty(2 * max_rows, dtype=torch.int32).pin_memory()
+
+    def sample_device(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
+                      steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> None:
+        """Fill self.tokens[:n] and self.flags[:n] for the n rows of `logits`."""
+        n = logits.shape[0]
+        assert n <= self.max_rows and logits.shape[1] == self.vocab
+        if params.temperature <= 0.0 and (params.repetition_penalty == 1.0 or not histories):
+            ops.argmax(logits, self.tokens, self.flags, n)
+            return
+        u = np.asarray([uniform(params.seed, r, s) for r, s in zip(requests, steps)], dtype=np.float32)
+        self.uniforms[:n].copy_(torch.from_numpy(u))
+        hist = hlen = None
+        if params.repetition_penalty != 1.0 and params.repetition_window > 0 and histories is not None:
+            w = min(params.repetition_window, self.history_cap)
+            rows = np.zeros((n, self.history_cap), dtype=np.int32)
+            lens = np.zeros(n, dtype=np.int32)
+            for i, h in enumerate(histories):
+                tail = list(h[-w:]) if w else []
+                rows[i, :len(tail)] = tail
+                lens[i] = len(tail)
+            self.history[:n].copy_(torch.from_numpy(rows))
+            self.history_len[:n].copy_(torch.from_numpy(lens))
+            hist, hlen = self.history, self.history_len
+        if self._probs is None or self._probs.numel() < n * self.vocab:
+            self._probs = torch.empty(self.max_rows * self.vocab, dtype=torch.float32, device=self.device)
+        ops.sample(logits, self.uniforms, self.tokens, self._probs, params.temperature, params.top_p,
+                   params.min_p, params.repetition_penalty, min(params.repetition_window, self.history_cap),
+                   hist, hlen, self.flags, n)
+
+    def sample(self, logits, params, requests, steps, histories=None) -> tuple[list[int], list[int]]:
+        n = logits.shape[0]
+        self.sample_device(logits, params, requests, steps, histories)
+        self._out_host[:n].copy_(self.tokens[:n], non_blocking=True)
+        self._out_host[self.max_rows:self.max_rows + n].copy_(self.flags[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._out_host[:n].tolist(), self._out_host[self.max_rows:self.max_rows + n].tolist()

@@ -1,0 +1,131 @@
+"""Generation through the Python entry point and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from plain_llama import plain_forward, plain_generate, plain_sample
+from tiny import TINY_A, TINY_B, TINY_C, make_model
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def prompts_for(cfg, lengths, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+
+
+def test_greedy_generation_matches_the_plain_implementation():
+    """Tiny A, float32: prompts of 5, 11 and 17 tokens, 8 greedy tokens each."""
+    import mdma_b200
+    d, c, tensors = make_model(TINY_A, 0, torch.float32)
+    prompts = prompts_for(TINY_A, (5, 11, 17), 0)
+    outs = mdma_b200.generate(d, prompts, max_tokens=8, temperature=0.0, dtype="float32", max_batch=3)
+    for p, o in zip(prompts, outs):
+        assert o.tokens == plain_generate(c, tensors, p, 8)
+        assert o.finish_reason == "length" and o.prompt_tokens == p
+
+
+def test_batches_one_after_another_and_stop_tokens():
+    import mdma_b200
+    d, c, tensors = make_model(TINY_C, 2, torch.float32)
+    prompts = prompts_for(TINY_C, (3, 40, 9, 1, 22), 5)
+    free = [plain_generate(c, tensors, p, 6) for p in prompts]
+    stop = [free[1][2], free[3][0]]                    # ends request 1 after two tokens, request 3 at once
+    outs = mdma_b200.generate(d, prompts, max_tokens=6, dtype="float32", max_batch=2, stop_ids=stop)
+    for p, o in zip(prompts, outs):
+        want = plain_generate(c, tensors, p, 6, stop_ids=stop)
+        assert o.tokens == want
+        assert o.finish_reason == ("stop" if len(want) < 6 else "length")
+
+
+def test_sampled_generation_is_seeded_and_independent_of_batch_mates():
+    """Tiny B, bfloat16 weights: 4 prompts of 1, 7, 32 and 60 tokens, 16 tokens at temperature 0.8."""
+    import mdma_b200
+    d, c, tensors = make_model(TINY_B, 1, torch.bfloat16)
+    prompts = prompts_for(TINY_B, (1, 7, 32, 60), 1)
+    kw = dict(max_tokens=16, temperature=0.8, top_p=0.95, min_p=0.05, repetition_penalty=1.1, seed=11)
+    for dtype in ("float32", "bfloat16"):
+        a = mdma_b200.generate(d, prompts, dtype=dtype, max_batch=4, **kw)
+        b = mdma_b200.generate(d, prompts, dtype=dtype, max_batch=4, **kw)
+        assert [o.tokens for o in a] == [o.tokens for o in b]
+        assert all(len(o.tokens) == 16 for o in a)
+    other = mdma_b200.generate(d, prompts, dtype="float32", max_batch=4, **{**kw, "seed": 12})
+    f32 = mdma_b200.generate(d, prompts, dtype="float32", max_batch=4, **kw)
+    assert [o.tokens for o in other] != [o.tokens for o in f32]
+    # request 2 alone, given its place in the list, draws the same tokens as inside the batch
+    from mdma_b200.engine import Engine
+    from mdma_b200.engine.generate import Generator
+    from mdma_b200.sampling import SamplingParams, uniform
+    from mdma_b200.sampling.sampler import DeviceSampler
+    # and the tokens follow the plain sampler on the plain model's logits
+    params = SamplingParams(0.8, 0.95, 0.05, 1.1, 64, 11)
+    W = {k: v.float() for k, v in tensors.items()}
+    seq = list(prompts[2])
+    for step in range(4):
+        logits = plain_forward(c, W, seq, torch.float32)[-1]
+        tok = plain_sample(logits.tolist(), seq, uniform(11, 2, step), 0.8, 0.95, 0.05, 1.1, 64)
+        assert tok == f32[2].tokens[step], step
+        seq.append(tok)
+
+
+def test_command_line(tmp_path):
+    d, c, tensors = make_model(TINY_A, 0, torch.float32)
+    p = prompts_for(TINY_A, (6,), 3)[0]
+    want = plain_generate(c, tensors, p, 5)
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mdma"), "run", d, ",".join(map(str, p)),
+                          "--max-tokens", "5", "--dtype", "float32", "--json"], capture_output=True, text=True, env=env)
+    assert res.returncode == 0, res.stderr
+    out = json.loads(res.stdout.strip().splitlines()[-1])
+    assert out["tokens"] == want and out["prompt_tokens"] == p and out["finish_reason"] == "length"
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mdma-run"), d, " ".join(map(str, p)), "5"],
+                         capture_output=True, text=True, env=dict(env, MDMA_JSON="1"))
+    assert res.returncode == 0, res.stderr
+    assert json.loads(res.stdout.strip().splitlines()[-1])["tokens"][:5] == json.loads(
+        subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mdma"), "run", d, ",".join(map(str, p)),
+                        "--max-tokens", "5", "--json"], capture_output=True, text=True, env=env).stdout.strip().splitlines()[-1])["tokens"]
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mdma"), "plan", d, "--ctx", "64", "--json"],
+                         capture_output=True, text=True, env=env)
+    plan = json.loads(res.stdout)
+    assert plan["total_bytes"] == plan["weights_bytes"] + plan["cache_bytes"] + plan["workspace_bytes"]
+
+
+def test_engine_refuses_bad_steps_and_keeps_its_cache():
+    from mdma_b200.engine import Engine, StepEntry, StepError
+    d, c, tensors = make_model(TINY_A, 0, torch.float32)
+    eng = Engine(d, dtype="float32", max_batch=2, max_context=64)
+    s = eng.acquire()
+    eng.step([StepEntry(s, [1, 2, 3], [2])])
+    for bad in ([StepEntry(s, [999], [0])], [StepEntry(s, [], [])], [StepEntry(s, [1], [1])],
+                [StepEntry(5, [1], [0])], [StepEntry(s, [1], [0]), StepEntry(s, [2], [0])],
+                [StepEntry(s, [1] * 62, [0])], []):
+        with pytest.raises(StepError):
+            eng.step(bad)
+        assert eng.cache.length(s) == 3
+        eng.cache.check()
+    ref = plain_forward(c, tensors, [1, 2, 3, 4], torch.float64)[-1]
+    got = eng.step([StepEntry(s, [4], [0])])[0].double().cpu()
+    assert (got - ref).abs().max() < 2e-5
+
+
+def test_memory_plan_refuses_what_does_not_fit():
+    from mdma_b200.engine import Engine, MemoryBudgetError
+    d, _, _ = make_model(TINY_A, 0, torch.float32)
+    with pytest.raises(MemoryBudgetError) as e:
+        Engine(d, dtype="float32", max_batch=2, vram_bytes=1 << 20, reserve_mib=0)
+    assert e.value.requested > e.value.available
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from mdma_b200.csrc import build
+    monkeypatch.setattr(build, "_loaded", {})
+    monkeypatch.setattr(build, "library_path", lambda name: "/nonexistent/lib.so")
+    monkeypatch.setattr(build, "find_nvcc", lambda: (_ for _ in ()).throw(build.BuildError("nvcc was not found")))
+    from mdma_b200 import ops
+    with pytest.raises(build.BuildError):
+        ops.argmax(torch.zeros(1, 4, device="cuda:0"), torch.zeros(1, dtype=torch.int32, device="cuda:0"))

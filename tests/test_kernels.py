@@ -1,0 +1,342 @@
+"""Each kernel alone against a plain PyTorch float32/float64 statement of the same
+operation, at sizes other than the engine tests use: tails that are no multiple
+of a tile, widths and vocabularies that are no power of two, a canary after
+every output."""
+import math
+
+import pytest
+import torch
+
+from plain_llama import plain_attention, plain_inv_freq, plain_rmsnorm, plain_rope, plain_sample
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops_mod():
+    from mdma_b200 import ops
+    return ops
+
+
+def close(got, want, atol, rtol=0.0):
+    got, want = got.double().cpu(), want.double().cpu()
+    assert torch.isfinite(got).all(), "non-finite output"
+    err = (got - want).abs()
+    bound = atol + rtol * want.abs()
+    assert bool((err <= bound).all()), f"max err {err.max().item():.3g} (bound {atol:.3g}+{rtol:.3g}*|x|)"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(dtype):
+    ops = ops_mod()
+    table = torch.randn(331, 120, device=DEV).to(dtype)
+    ids = torch.tensor([0, 330, 7, 7, 119], dtype=torch.int32, device=DEV)
+    out = torch.full((7, 120), 9.0, device=DEV)
+    ops.embed_rows(table, ids, out)
+    close(out[:5], table[ids.long()].float(), 0.0)
+    assert bool((out[5:] == 9.0).all())
+
+
+@pytest.mark.parametrize("width", [4099, 96, 8])
+@pytest.mark.parametrize("odt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+def test_rmsnorm(width, odt, wdt):
+    ops = ops_mod()
+    torch.manual_seed(width)
+    x = torch.randn(6, width, device=DEV) * 3 + 0.5
+    w = (torch.randn(width, device=DEV) * 0.5 + 1).to(wdt)
+    out = torch.full((5, width), 9.0, device=DEV, dtype=odt)
+    ops.rmsnorm(x, w, 3e-6, out, n_rows=4)
+    want = plain_rmsnorm(x[:4].double().cpu(), w.double().cpu(), 3e-6)
+    close(out[:4], want, 1e-5 if odt == torch.float32 else 0, 0 if odt == torch.float32 else 1e-2)
+    assert bool((out[4:] == 9.0).all())
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    ops.rmsnorm(x, w, 3e-6, out, rows=rows)
+    want = plain_rmsnorm(x[[5, 0, 5]].double().cpu(), w.double().cpu(), 3e-6)
+    close(out[:3], want, 1e-5 if odt == torch.float32 else 0, 0 if odt == torch.float32 else 1e-2)
+
+
+def paged_cache(n_pages, page, kvh, d, dtype):
+    k = torch.zeros(n_pages, page, kvh, d, device=DEV, dtype=dtype)
+    return k, torch.zeros_like(k)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("layout,hd,rot", [("interleaved", 48, 48), ("split_half", 80, 80), ("split_half", 64, 32)])
+def test_rope_cache_write(dtype, layout, hd, rot):
+    """Positions up to 30,000 with theta 1e6 (the reference's hard case,
+    src/backend/cuda/tests.rs:601-647); scattered pages; partial rotary width."""
+    ops = ops_mod()
+    torch.manual_seed(0)
+    H, K, page, max_pages = 3, 2, 16, 2048
+    pos = [0, 1, 17, 30000, 29999, 5]
+    seq = [0, 0, 0, 1, 1, 2]
+    T = len(pos)
+    qkv = torch.randn(T, (H + 2 * K) * hd, device=DEV).to(dtype)
+    orig = qkv.clone()
+    inv = plain_inv_freq(rot, 1e6, None).to(DEV)
+    kc, vc = paged_cache(40, page, K, hd, dtype)
+    table = torch.zeros(3, max_pages, dtype=torch.int32, device=DEV)
+    table[0, 0], table[0, 1], table[1, 29999 // page], table[1, 30000 // page], table[2, 0] = 7, 3, 11, 30, 1
+    slots = torch.tensor([0, 1, 2], dtype=torch.int32, device=DEV)
+    ops.rope_cache_write(qkv, T, torch.tensor(seq, dtype=torch.int32, device=DEV),
+                         torch.tensor(pos, dtype=torch.int32, device=DEV), slots, inv, kc, vc, table,
+                         max_pages, page, H, K, hd, rot, layout == "interleaved", True)
+    o = orig.double().cpu().reshape(T, H + 2 * K, hd)
+    p = torch.tensor(pos)
+    want_q = o[:, :H].clone()
+    want_k = o[:, H:H + K].clone()
+    want_q[..., :rot] = plain_rope(o[:, :H, :rot], p, inv.cpu(), layout)
+    want_k[..., :rot] = plain_rope(o[:, H:H + K, :rot], p, inv.cpu(), layout)
+    tol = dict(atol=2e-6) if dtype == torch.float32 else dict(atol=2e-2, rtol=1e-2)
+    close(qkv.reshape(T, H + 2 * K, hd)[:, :H], want_q, **tol)
+    assert torch.equal(qkv.reshape(T, H + 2 * K, hd)[:, H:], orig.reshape(T, H + 2 * K, hd)[:, H:])
+    used = set()
+    for t in range(T):
+        pg = int(table[seq[t], pos[t] // page])
+        used.add((pg, pos[t] % page))
+        close(kc[pg, pos[t] % page], want_k[t], **tol)
+        close(vc[pg, pos[t] % page], o[t, H + K:], 0.0)
+    mask = torch.ones(40, page, dtype=torch.bool)
+    for pg, r in used:
+        mask[pg, r] = False
+    assert bool((kc.cpu()[mask] == 0).all()) and bool((vc.cpu()[mask] == 0).all())   # nothing else written
+
+
+def fill_cache(seq_lens, K, hd, page, dtype, seed=0, scatter=True):
+    """Random keys/values for sequences, stored in shuffled pages. Returns dense and paged forms."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages_each = [-(-n // page) for n in seq_lens]
+    total = sum(n_pages_each) + 3
+    order = torch.randperm(total, generator=g).tolist() if scatter else list(range(total))
+    kc, vc = paged_cache(total, page, K, hd, dtype)
+    max_pages = max(n_pages_each) + 1
+    table = torch.zeros(len(seq_lens), max_pages, dtype=torch.int32)
+    dense = []
+    cur = 0
+    for s, n in enumerate(seq_lens):
+        k = torch.randn(n, K, hd, generator=g).to(dtype)
+        v = torch.randn(n, K, hd, generator=g).to(dtype)
+        dense.append((k, v))
+        for pi in range(n_pages_each[s]):
+            pg = order[cur]; cur += 1
+            table[s, pi] = pg
+            rows = slice(pi * page, min(n, (pi + 1) * page))
+            kc[pg, : rows.stop - rows.start] = k[rows].to(DEV)
+            vc[pg, : rows.stop - rows.start] = v[rows].to(DEV)
+    return kc, vc, table.to(DEV), max_pages, dense
+
+
+def reference_attention(q, dense, tok_seq, tok_pos, scale, window):
+    """q [T,H,D] float64; for each token attend over its sequence's keys [first, pos]."""
+    T, H, D = q.shape
+    out = torch.zeros(T, H * D, dtype=torch.float64)
+    for t in range(T):
+        k, v = dense[tok_seq[t]]
+        n = tok_pos[t] + 1
+        # plain_attention on a one-query problem: put the query last
+        qq = torch.zeros(n, H, D, dtype=torch.float64)
+        qq[-1] = q[t]
+        out[t] = plain_attention(qq, k[:n].double(), v[:n].double(), scale, window)[-1]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,K,hd,window", [(6, 2, 48, 0), (4, 4, 16, 0), (8, 1, 128, 0), (6, 3, 80, 37), (5, 5, 256, 0)])
+def test_attention_simple(dtype, H, K, hd, window):
+    ops = ops_mod()
+    torch.manual_seed(1)
+    page = 16
+    seq_lens = [300, 41, 1]
+    kc, vc, table, max_pages, dense = fill_cache(seq_lens, K, hd, page, dtype)
+    tok_seq = [0, 0, 0, 1, 1, 2]
+    tok_pos = [299, 150, 0, 40, 16, 0]
+    T = len(tok_seq)
+    q = torch.randn(T, H * hd + 24, device=DEV).to(dtype)          # padded row: queries are a prefix
+    out = torch.full((T + 1, H * hd), 9.0, device=DEV, dtype=dtype)
+    scale = 0.77 / math.sqrt(hd)
+    ops.attention_simple(q, T, kc, vc, torch.tensor(tok_seq, dtype=torch.int32, device=DEV),
+                         torch.tensor(tok_pos, dtype=torch.int32, device=DEV),
+                         torch.arange(3, dtype=torch.int32, device=DEV), table, max_pages, page, out,
+                         H, K, hd, window, scale)
+    want = reference_attention(q[:, :H * hd].double().cpu().reshape(T, H, hd), dense, tok_seq, tok_pos, scale, window)
+    close(out[:T], want, 2e-5 if dtype == torch.float32 else 3e-2)
+    assert bool((out[T:] == 9.0).all())
+
+
+def test_attention_finds_one_far_key():
+    """One key among hundreds is made to dominate; random weights would hide a miss."""
+    ops = ops_mod()
+    H, K, hd, page = 2, 1, 32, 16
+    kc, vc, table, max_pages, dense = fill_cache([700], K, hd, page, torch.float32, seed=3)
+    k, v = dense[0]
+    q = torch.randn(1, H * hd)
+    target = 123
+    k[target, 0] = q[0, :hd] * 4.0                               # head 0 points at key 123
+    pg = int(table[0, target // page])
+    kc[pg, target % page, 0] = k[target, 0].to(DEV)
+    out = torch.zeros(1, H * hd, device=DEV)
+    ops.attention_simple(q.to(DEV), 1, kc, vc, torch.zeros(1, dtype=torch.int32, device=DEV),
+                         torch.tensor([699], dtype=torch.int32, device=DEV),
+                         torch.zeros(1, dtype=torch.int32, device=DEV), table, max_pages, page, out,
+                         H, K, hd, 0, 1.0)
+    close(out[0, :hd], v[target, 0], 1e-4)                      # softmax is one-hot on the far key
+    want = reference_attention(q.double().reshape(1, H, hd), dense, [0], [699], 1.0, 0)
+    close(out, want, 2e-5)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 5, 3), (67, 130, 100), (5, 331, 120), (200, 64, 17)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_gemm_simt(M, N, K, dt):
+    ops = ops_mod()
+    torch.manual_seed(M)
+    a = torch.randn(M + 1, K + 8, device=DEV).to(dt)[:, :K]      # a pitch wider than K
+    w = (torch.randn(N, K, device=DEV) * 0.1).to(dt)
+    w2 = (torch.randn(N, K, device=DEV) * 0.1).to(dt)
+    ref = a[:M].double() @ w.double().t()
+    tol = dict(atol=1e-5) if dt == torch.float32 else dict(atol=2e-2, rtol=1e-2)
+    out = torch.full((M + 1, N), 9.0, device=DEV, dtype=dt)
+    ops.gemm_simt(a, w, out, ops.GEMM_STORE, None, M)
+    close(out[:M], ref, **tol)
+    assert bool((out[M:] == 9.0).all())
+    x = torch.randn(M + 1, N, device=DEV)
+    x0 = x.clone()
+    if dt == torch.bfloat16:
+        ops.gemm_simt(a, w, x, ops.GEMM_ACCUMULATE, None, M)
+        close(x[:M], x0[:M].double() + ref, 1e-5 * K)
+        assert torch.equal(x[M:], x0[M:])
+    ref2 = a[:M].double() @ w2.double().t()
+    ops.gemm_simt(a, w, out, ops.GEMM_SWIGLU, w2, M)
+    close(out[:M], ref / (1 + torch.exp(-ref)) * ref2, **tol)
+
+
+def test_gemm_simt_rows_do_not_depend_on_their_neighbours():
+    ops = ops_mod()
+    a = torch.randn(70, 96, device=DEV)
+    w = torch.randn(50, 96, device=DEV)
+    big = torch.empty(70, 50, device=DEV)
+    one = torch.empty(1, 50, device=DEV)
+    ops.gemm_simt(a, w, big)
+    ops.gemm_simt(a[37:38], w, one)
+    assert torch.equal(big[37:38], one)                           # bitwise: fixed order of additions
+
+
+@pytest.mark.parametrize("M,N,K,mode", [(1, 128, 64, 0), (9, 200, 72, 0), (130, 1000, 1032, 0), (600, 264, 256, 0),
+                                        (7, 520, 2048, 1), (300, 136, 512, 1), (3, 300, 264, 2), (257, 384, 640, 2),
+                                        (2, 331, 8, 0)])
+def test_gemm_tensor(M, N, K, mode):
+    from mdma_b200 import ops_tensor
+    ops = ops_mod()
+    torch.manual_seed(N)
+    a = (torch.randn(M + 3, K + 16, device=DEV) * 0.5).bfloat16()[:, :K]
+    w = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    w2 = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    ref = a[:M].double() @ w.double().t()
+    if mode == 1:
+        x = torch.randn(M + 2, N, device=DEV)
+        x0 = x.clone()
+        ops_tensor.gemm(a, w, x, ops.GEMM_ACCUMULATE, None, M)
+        close(x[:M], x0[:M].double() + ref, 2e-5 * max(K, 64) ** 0.5 + 1e-5)
+        assert torch.equal(x[M:], x0[M:])
+    else:
+        for odt in (torch.bfloat16, torch.float32) if mode == 0 else (torch.bfloat16,):
+            out = torch.full((M + 2, N), 9.0, device=DEV, dtype=odt)
+            ops_tensor.gemm(a, w, out, mode, w2 if mode == 2 else None, M)
+            want = ref if mode == 0 else ref / (1 + torch.exp(-ref)) * (a[:M].double() @ w2.double().t())
+            close(out[:M], want, 1e-4 if odt == torch.float32 else 1e-2, 0 if odt == torch.float32 else 1e-2)
+            assert bool((out[M:] == 9.0).all())
+    ops_tensor.check_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("splits", [2, 3, 7])
+def test_gemm_tensor_split_k_is_reproducible(splits):
+    from mdma_b200 import ops_tensor
+    ops = ops_mod()
+    a = (torch.randn(5, 1024, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(200, 1024, device=DEV) * 0.1).bfloat16()
+    ref = a.double() @ w.double().t()
+    outs = []
+    for _ in range(2):
+        out = torch.zeros(5, 200, device=DEV)
+        ops_tensor.gemm(a, w, out, ops.GEMM_STORE, None, 5, bn=16, splits=splits)
+        outs.append(out)
+    close(outs[0], ref, 1e-4)
+    assert torch.equal(outs[0], outs[1])
+    ops_tensor.check_status(torch.device(DEV))
+
+
+def test_gemm_tensor_refuses_what_it_cannot_do():
+    from mdma_b200 import ops_tensor
+    from mdma_b200.ops import KernelError
+    a = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(16, 100, device=DEV, dtype=torch.bfloat16)
+    assert not ops_tensor.gemm_supported(16, 100)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        ops_tensor.gemm(a, w, torch.zeros(4, 16, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(KernelError, match="bfloat16"):
+        ops_tensor.gemm(a.float(), w.float(), torch.zeros(4, 16, device=DEV))
+
+
+def test_kernels_refuse_cpu_tensors():
+    ops = ops_mod()
+    from mdma_b200.ops import KernelError
+    with pytest.raises(KernelError, match="no CPU path"):
+        ops.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-5, torch.zeros(2, 8))
+
+
+def test_argmax_lowest_index_and_flags():
+    ops = ops_mod()
+    logits = torch.randn(5, 33001, device=DEV)
+    logits[0, 777] = logits[0, 31000] = 50.0                      # tie: the lowest index
+    logits[1, 33000] = 60.0                                       # last element
+    logits[2, 5] = float("nan")
+    logits[3, 9] = float("inf")
+    tok = torch.zeros(6, dtype=torch.int32, device=DEV)
+    flags = torch.zeros(6, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, tok, flags, 5)
+    assert tok[:2].tolist() == [777, 33000] and int(tok[4]) == int(logits[4].argmax())
+    assert flags[:5].tolist() == [0, 0, 1, 1, 0]
+
+
+@pytest.mark.parametrize("vocab", [331, 5000])
+@pytest.mark.parametrize("opts", [dict(temperature=0.8, top_p=0.95, min_p=0.05, repetition_penalty=1.1),
+                                  dict(temperature=1.3, top_p=1.0, min_p=0.0, repetition_penalty=1.0),
+                                  dict(temperature=0.5, top_p=0.3, min_p=0.0, repetition_penalty=1.0),
+                                  dict(temperature=1.0, top_p=1.0, min_p=0.2, repetition_penalty=1.5),
+                                  dict(temperature=0.0, top_p=1.0, min_p=0.0, repetition_penalty=1.7)])
+def test_sample_matches_the_host_sampler(vocab, opts):
+    """Same uniform number, same token as the plain sampler (src/sampler.rs:34-135)."""
+    ops = ops_mod()
+    torch.manual_seed(vocab)
+    n = 24
+    logits = torch.randn(n, vocab) * 3
+    logits[3, 10] = logits[3, 20] = logits[3].max() + 1           # tied leaders
+    hist = torch.randint(0, vocab, (n, 64), dtype=torch.int32)
+    hist[:, 0] = logits.argmax(1).int()                           # penalise the leader
+    hlen = torch.full((n,), 64, dtype=torch.int32)
+    u = torch.rand(n)
+    tok = torch.zeros(n, dtype=torch.int32, device=DEV)
+    flags = torch.zeros(n, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(n * vocab, device=DEV)
+    ops.sample(logits.to(DEV), u.to(DEV), tok, scratch, opts["temperature"], opts["top_p"], opts["min_p"],
+               opts["repetition_penalty"], 64, hist.to(DEV), hlen.to(DEV), flags)
+    want = [plain_sample(logits[i].tolist(), hist[i].tolist(), float(u[i]), opts["temperature"], opts["top_p"],
+                         opts["min_p"], opts["repetition_penalty"], 64) for i in range(n)]
+    got = tok.tolist()
+    mism = [i for i in range(n) if got[i] != want[i]]
+    assert not mism, f"rows {mism}: got {[got[i] for i in mism]}, want {[want[i] for i in mism]}"
+    assert flags.sum().item() == 0
+
+
+def test_sample_follows_the_distribution():
+    ops = ops_mod()
+    vocab, n = 50, 4000
+    row = torch.randn(vocab) * 2
+    logits = row.repeat(n, 1).to(DEV)
+    u = torch.rand(n, generator=torch.Generator().manual_seed(0)).to(DEV)
+    tok = torch.zeros(n, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(n * vocab, device=DEV)
+    ops.sample(logits, u, tok, scratch, 1.0, 1.0, 0.0, 1.0, 0)
+    freq = torch.bincount(tok.long().cpu(), minlength=vocab).double() / n
+    p = torch.softmax(row.double(), 0)
+    assert (freq - p).abs().max() < 4 * (p.max() * (1 - p.max()) / n) ** 0.5 + 0.01

@@ -1,0 +1,167 @@
+"""Generality of the parts: a toy mixer with state of its own, a toy
+architecture that mixes it with attention layers, runs one layer twice and lets
+one layer read another's cache — all defined here, registered, built from a
+model folder and stepped, without touching the framework's files."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from plain_llama import plain_attention, plain_inv_freq, plain_rmsnorm, plain_rope, plain_swiglu
+
+pytestmark = pytest.mark.gpu
+
+E, H, K, D, F, V = 48, 4, 2, 16, 72, 97
+
+
+def register_toy():
+    from mdma_b200.cache import StateNeed
+    from mdma_b200.config import Architecture
+    from mdma_b200.parts.base import Part
+    from mdma_b200.registry import ARCHITECTURES, MIXERS
+    from mdma_b200.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+
+    class DecayMixer(Part):
+        """s <- decay * s + W_in h_t;  x_t += W_out s.  The state s is per sequence, fixed size."""
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.width, self.inner, self.decay = spec.params["width"], spec.params["inner"], spec.params["decay"]
+
+        def tensor_specs(self):
+            return {"in.weight": TensorSpec((self.inner, self.width)), "out.weight": TensorSpec((self.width, self.inner))}
+
+        def kv_need(self):
+            return None
+
+        def state_need(self):
+            return StateNeed((self.inner,), torch.float32)
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.w_in, self.w_out = tensors["in.weight"].float(), tensors["out.weight"].float()
+
+        def forward(self, ctx, h, x, view, owns_cache=True):
+            u = h[:ctx.n_tokens].float() @ self.w_in.t()
+            row = 0
+            for slot, n in zip(ctx.host_seq_slot, ctx.host_seq_new):
+                s = view.state[slot]
+                for t in range(row, row + n):
+                    s.mul_(self.decay).add_(u[t])
+                    x[t] += self.w_out @ s
+                row += n
+
+    MIXERS.register("toy_decay", DecayMixer, replace=True)
+
+    def config_from_dict(d):
+        return dict(d)
+
+    def describe(c):
+        def norm(prefix):
+            return PartSpec("rmsnorm", dict(width=E, eps=c["eps"]), prefix=prefix)
+
+        def ffn(prefix):
+            return PartSpec("gated_mlp", dict(hidden_size=E, intermediate_size=F), prefix=prefix)
+        pos = PartSpec("rotary", dict(head_dim=D, rotary_dim=D, theta=c["theta"], layout="split_half", scaling=None))
+
+        def attn(prefix, shared):
+            return PartSpec("attention", dict(hidden_size=E, num_heads=H, num_kv_heads=K, head_dim=D,
+                                              scale=D ** -0.5, window=0, position=pos, shared_cache=shared), prefix=prefix)
+        layers = [
+            LayerSpec("prenorm", norm("l0.n1."), attn("l0.attn.", False), norm("l0.n2."), ffn("l0.mlp.")),
+            LayerSpec("prenorm", norm("l1.n1."), PartSpec("toy_decay", dict(width=E, inner=24, decay=c["decay"]),
+                                                           prefix="l1.mix."), norm("l1.n2."), ffn("l1.mlp.")),
+            LayerSpec("prenorm", norm("l2.n1."), attn("l2.attn.", True), norm("l2.n2."), ffn("l2.mlp.")),
+        ]
+        # layer 1 runs twice (two states); layer 2 reads the cache that entry 0 wrote
+        schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2, cache=0), ScheduleEntry(1)]
+        return ModelSpec(hidden_size=E, vocab_size=V, max_positions=256,
+                         embedding=PartSpec("embedding", dict(vocab_size=V, width=E), prefix="emb."),
+                         layers=layers, schedule=schedule, final_norm=norm("final."),
+                         lm_head=PartSpec("lm_head", dict(vocab_size=V, width=E), prefix="head."))
+
+    ARCHITECTURES.register("ToyMixedLM", Architecture("ToyMixedLM", config_from_dict, describe), replace=True)
+
+
+def plain_toy(c, W, ids):
+    """The same toy model, whole sequence, float64, written out by hand."""
+    W = {k: v.double() for k, v in W.items()}
+    T = len(ids)
+    x = W["emb.weight"][torch.tensor(ids)]
+    inv = plain_inv_freq(D, c["theta"], None)
+    pos = torch.arange(T)
+    kv = {}
+
+    def mlp(x, p):
+        h = plain_rmsnorm(x, W[p + "n2.weight"], c["eps"])
+        return x + plain_swiglu(h @ W[p + "mlp.gate_proj.weight"].t(), h @ W[p + "mlp.up_proj.weight"].t()) @ W[p + "mlp.down_proj.weight"].t()
+
+    def attn(x, p, shared):
+        h = plain_rmsnorm(x, W[p + "n1.weight"], c["eps"])
+        q = plain_rope((h @ W[p + "attn.q_proj.weight"].t()).reshape(T, H, D), pos, inv, "split_half")
+        if not shared:
+            kv["k"] = plain_rope((h @ W[p + "attn.k_proj.weight"].t()).reshape(T, K, D), pos, inv, "split_half")
+            kv["v"] = (h @ W[p + "attn.v_proj.weight"].t()).reshape(T, K, D)
+        return x + plain_attention(q, kv["k"], kv["v"], D ** -0.5) @ W[p + "attn.o_proj.weight"].t()
+
+    def decay(x, p):
+        h = plain_rmsnorm(x, W[p + "n1.weight"], c["eps"])
+        u = h @ W[p + "mix.in.weight"].t()
+        s = torch.zeros(24, dtype=torch.float64)
+        out = x.clone()
+        for t in range(T):
+            s = c["decay"] * s + u[t]
+            out[t] = x[t] + W[p + "mix.out.weight"] @ s
+        return out
+
+    x = mlp(attn(x, "l0.", False), "l0.")
+    x = mlp(decay(x, "l1."), "l1.")
+    x = mlp(attn(x, "l2.", True), "l2.")
+    x = mlp(decay(x, "l1."), "l1.")
+    return plain_rmsnorm(x, W["final.weight"], c["eps"]) @ W["head.weight"].t()
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 6e-2)])
+def test_toy_architecture_builds_and_steps(tmp_path, dtype, tol):
+    register_toy()
+    from mdma_b200.engine import Engine, StepEntry
+    from mdma_b200.weights import write_random_model
+    from mdma_b200.weights.safetensors_io import SafetensorsFile
+    cfg = dict(architectures=["ToyMixedLM"], eps=1e-5, theta=5000.0, decay=0.8)
+    d = write_random_model(str(tmp_path / "toy"), cfg, 7, torch.float32)
+    sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    W = {n: sf.tensor(n).clone() for n in sf.entries}
+    assert "l2.attn.k_proj.weight" not in W and "l1.mix.in.weight" in W     # the sharing layer owns no k/v
+    eng = Engine(d, dtype=dtype, max_batch=3, max_context=128)
+    assert len(eng.cache.groups) == 1 and eng.cache.groups[0].sites == [0]  # one cache site, read twice
+    assert sorted(eng.cache.states) == [1, 3]                               # two runs, two states
+    g = torch.Generator().manual_seed(0)
+    seqs = [torch.randint(0, V, (n,), generator=g).tolist() for n in (33, 9, 70)]
+    ref = [plain_toy(cfg, W, s).numpy() for s in seqs]
+    # whole prompts of unequal length in one step
+    slots = [eng.acquire() for _ in seqs]
+    out = eng.step([StepEntry(sl, s, list(range(len(s)))) for sl, s in zip(slots, seqs)]).cpu().numpy()
+    off = 0
+    for s, r in zip(seqs, ref):
+        assert np.abs(out[off:off + len(s)] - r).max() < tol
+        off += len(s)
+    for sl in slots:
+        eng.release(sl)
+    # a prompt, then one token each; the second batch reuses the slots (state must start from zero)
+    slots = [eng.acquire() for _ in seqs]
+    cut = [len(s) // 2 for s in seqs]
+    eng.step([StepEntry(sl, s[:c], []) for sl, s, c in zip(slots, seqs, cut)])
+    pos = list(cut)
+    live = list(range(len(seqs)))
+    while live:
+        out = eng.step([StepEntry(slots[i], [seqs[i][pos[i]]], [0]) for i in live]).cpu().numpy()
+        for row, i in enumerate(live):
+            assert np.abs(out[row] - ref[i][pos[i]]).max() < tol, (i, pos[i])
+            pos[i] += 1
+        for i in [i for i in live if pos[i] == len(seqs[i])]:
+            eng.release(slots[i])
+        live = [i for i in live if pos[i] < len(seqs[i])]
+    eng.cache.check()
