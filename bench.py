@@ -1,0 +1,252 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens/s and prefill tokens/s at the Llama-3.1-8B shape.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line.  The default run has the layer sizes of the
+Llama-3.1-8B shape with random bfloat16 weights, a batch of 8 sequences
+decoding after 512-token prompts in a cache sized for a context of 4096.  A
+"step" is one decode step of the whole batch (forward, token selection,
+feeding the tokens back).  `value` is timed on the device with CUDA events
+around exactly K steps; `e2e` is the same through the Python entry point
+(`Generator.generate`, host token lists in and out).  Decoding streams 15 GB
+of weights per step, far more than the 126 MB L2, so nothing is flushed
+between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_31_8B = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=32, hidden_size=4096,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
+    rope_theta=500000.0, rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                                           high_freq_factor=4.0, original_max_position_embeddings=8192),
+    rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=131072)
+FULL_LAYERS = 32
+
+
+def peaks():
+    """Measured peaks if the driver wrote them, else the stated fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    hbm, tf, src = 6650.0, 1590.0, "fallback"
+    if os.path.isfile(path):
+        try:
+            d = json.load(open(path))
+            hbm = float(d.get("hbm_gbs", hbm))
+            tf = float(d.get("bf16_tflops", tf))
+            src = "measured"
+        except (ValueError, OSError):
+            pass
+    return hbm, tf, src
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(int(float(s[0])) for s in self.samples if s[0].replace(".", "").isdigit())
+        mx = [int(float(s[1])) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[3:7]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def matmul_params(cfg, layers):
+    E, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = E * (q + 2 * kv) + q * E + 3 * E * F
+    return layers * per_layer, V * E
+
+
+def prefill_flops(cfg, layers, T):
+    body, head = matmul_params(cfg, layers)
+    attn = layers * 2 * 2 * cfg["num_attention_heads"] * cfg["head_dim"] * (T * (T + 1) // 2)
+    return 2 * T * body + 2 * head + attn          # the head runs on the last row only
+
+
+def decode_bytes(cfg, layers, batch, context):
+    body, head = matmul_params(cfg, layers)
+    kv_row = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * layers
+    return 2 * (body + head) + batch * context * kv_row
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the shape has (named in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "AliOsm/mdma is a Rust crate (Cargo.toml, no setup.py/pyproject.toml); pip cannot "
+                          "install it and no cargo/rustc is in the image"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not built in this library")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+    from mdma_b200 import ops
+    from mdma_b200.engine import Engine, StepEntry
+    from mdma_b200.engine.generate import Generator
+    from mdma_b200.sampling import SamplingParams
+    from mdma_b200.sampling.sampler import DeviceSampler
+
+    cfg = dict(LLAMA_31_8B, num_hidden_layers=args.layers)
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    torch.cuda.set_device(0)
+    max_batch = max(args.batch, 1 if args.no_points else 64)
+    eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_batch=max_batch, max_context=args.context)
+    sampler = DeviceSampler(eng.vocab_size, eng.max_slots, eng.device)
+    gen = torch.Generator().manual_seed(0)
+
+    def prompts(n, length):
+        return [torch.randint(0, cfg["vocab_size"], (length,), generator=gen).tolist() for _ in range(n)]
+
+    def time_decode(batch, steps):
+        """Device time of `steps` decode steps of `batch` sequences after prompt_len-token prompts."""
+        slots = [eng.acquire() for _ in range(batch)]
+        ps = prompts(batch, args.prompt_len)
+        logits = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, ps)])
+        toks, _ = sampler.sample(logits, SamplingParams.greedy(), list(range(batch)), [0] * batch)
+        sess = eng.decode_session(sampler, SamplingParams.greedy())
+        sess.start(slots, toks)
+        for _ in range(warmup):
+            sess.step_async()
+        torch.cuda.synchronize()
+        launches0 = ops.LAUNCHES
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            sess.step_async()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        per_graph = sess.launches_per_step
+        ctx_now = args.prompt_len + warmup + steps
+        for s in slots:
+            eng.release(s)
+        return ms / steps, per_graph * steps, ctx_now
+
+    clock = ClockSampler()
+    clock.start()
+    ms_step, launches, ctx_end = time_decode(args.batch, args.steps)
+    clocks = clock.stop()
+    value = args.batch * 1000.0 / ms_step
+    avg_ctx = args.prompt_len + warmup + args.steps / 2
+    bytes_step = decode_bytes(cfg, args.layers, args.batch, avg_ctx)
+    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+
+    # end to end: host token lists in, host token lists out, through Generator.generate
+    stamps = []
+    g = Generator(eng, sampler)
+    n_e2e = args.steps + warmup + 1
+    g.generate(prompts(args.batch, args.prompt_len), max_tokens=warmup + 2)        # warm the path
+    g.generate(prompts(args.batch, args.prompt_len), max_tokens=n_e2e,
+               on_token=lambda r, t: stamps.append(time.perf_counter()) if r == args.batch - 1 else None)
+    # stamps[i] is taken after every sequence's i-th token reached the host
+    e2e_tokens = args.batch * args.steps
+    e2e_value = e2e_tokens / (stamps[-1] - stamps[-1 - args.steps])
+    e2e = {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
+           "d2h_bytes_per_step": 8 * args.batch}
+
+    out = {
+        "metric": "decode tokens/s (Llama-3.1-8B shape, batch 8, after 512-token prompts)",
+        "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (uniform random token ids, random N(0,0.02) weights)",
+        "impl": "ours",
+        "config": {"model": "Llama-3.1-8B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": args.batch, "seq_len": args.context, "prompt_len": args.prompt_len,
+                   "context_at_end": ctx_end, "parallelism": "single GPU", "page_size": eng.page_size,
+                   "cuda_graph": True, "l2": "inputs (15 GB of weights per step) larger than L2, no flush",
+                   "peaks": peak_src},
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": round(achieved / hbm_gbs, 4)},
+    }
+
+    if not args.no_points:
+        points = {}
+        for b in (1, 64):
+            ms_b, _, _ = time_decode(b, max(8, args.steps // 2))
+            points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 2)
+        out["points"] = points
+        # prefill of 2,048 tokens
+        T = 2048
+        times = []
+        for i in range(warmup + 5):
+            s = eng.acquire()
+            p = prompts(1, T)[0]
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([StepEntry(s, p, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            eng.release(s)
+            if i >= warmup:
+                times.append(e0.elapsed_time(e1))
+        ms_p = sorted(times)[len(times) // 2]
+        fl = prefill_flops(cfg, args.layers, T)
+        out["prefill"] = {"value": round(T * 1000.0 / ms_p, 1), "tokens": T, "ms": round(ms_p, 3),
+                          "frac": round(fl / (ms_p * 1e-3) / (bf16_tflops * 1e12), 4)}
+    from mdma_b200 import ops_tensor
+    ops_tensor.check_status(eng.device)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -98,11 +98,29 @@ __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restric
     for (int e = threadIdx.x; e < width; e += blockDim.x) yr[e] = xr[e];
 }
 
+// After a decode step: the sampled tokens become the next inputs and every
+// position moves on by one.
+__global__ void advance_decode_kernel(const int* __restrict__ tokens, int* __restrict__ ids,
+                                      int* __restrict__ tok_pos, int* __restrict__ seq_pos0, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    ids[i] = tokens[i];
+    tok_pos[i] += 1;
+    seq_pos0[i] += 1;
+}
+
 }  // namespace mdma
 
 using namespace mdma;
 
 extern "C" {
+
+int mdma_advance_decode(const int* tokens, int* ids, int* tok_pos, int* seq_pos0, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    advance_decode_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, ids, tok_pos, seq_pos0, n);
+    MDMA_LAUNCH_OK("advance_decode");
+    return 0;
+}
 
 const char* mdma_last_error() { return error_buffer(); }
 

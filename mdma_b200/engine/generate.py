@@ -66,8 +66,9 @@ def token_budget(prompt_len: int, max_tokens: int, max_context: int) -> tuple[in
 
 
 class Generator:
-    def __init__(self, engine, sampler):
-        self.engine, self.sampler = engine, sampler
+    def __init__(self, engine, sampler, use_graphs: bool = True):
+        self.engine, self.sampler, self.use_graphs = engine, sampler, use_graphs
+        self._sessions: dict = {}
 
     def plan_batches(self, sizes: Sequence[tuple[int, int]]) -> list[list[int]]:
         """Cut request indices, in order, into batches the cache can hold at once."""
@@ -105,19 +106,30 @@ class Generator:
 
     def _run_batch(self, batch, prompts, budgets, outputs, params, stop, cancelled, on_token) -> None:
         live = [_Live(r, self.engine.acquire(), budgets[r][0], budgets[r][1]) for r in batch]
+        penalised = params.repetition_penalty != 1.0 and params.repetition_window > 0
+        session = None
         try:
             entries = [StepEntry(s.slot, list(prompts[s.request]), [len(prompts[s.request]) - 1]) for s in live]
+            first = True
             while live:
                 if cancelled is not None and cancelled():
                     for s in live:
                         outputs[s.request].finish_reason = FINISH_CANCELLED
                     break
-                logits = self.engine.step(entries)
                 histories = None
-                if params.repetition_penalty != 1.0 and params.repetition_window > 0:
+                if penalised:
                     histories = [outputs[s.request].prompt_tokens + outputs[s.request].tokens for s in live]
-                tokens, flags = self.sampler.sample(logits, params, [s.request for s in live],
-                                                    [s.steps for s in live], histories)
+                if first or session is None:
+                    logits = self.engine.step(entries)
+                    tokens, flags = self.sampler.sample(logits, params, [s.request for s in live],
+                                                        [s.steps for s in live], histories)
+                else:
+                    # decode: this step's input tokens go up from the host, the step is replayed
+                    # as a graph, the selected tokens come back
+                    session.start([s.slot for s in live], [s.next_token for s in live],
+                                  [s.request for s in live], [s.steps for s in live])
+                    session.step_async(histories)
+                    tokens, flags = session.read_tokens()
                 survivors = []
                 for s, tok, bad in zip(live, tokens, flags):
                     out = outputs[s.request]
@@ -139,7 +151,15 @@ class Generator:
                     self.engine.release(s.slot)
                     s.slot = -1
                 live = survivors
-                entries = [StepEntry(s.slot, [s.next_token], [0]) for s in live]
+                if first and live and self.use_graphs and hasattr(self.engine, "decode_session"):
+                    session = self._sessions.get(params)
+                    if session is None:
+                        session = self._sessions[params] = self.engine.decode_session(self.sampler, params)
+                    if not session.graph_safe:
+                        session = None
+                first = False
+                if session is None:
+                    entries = [StepEntry(s.slot, [s.next_token], [0]) for s in live]
         finally:
             for s in live:
                 if s.slot >= 0:
@@ -151,7 +171,8 @@ def generate(model_dir: str, prompts: Sequence[Sequence[int]], max_tokens: int =
              temperature: float = 0.0, seed: int = 0, stop_ids: Optional[Sequence[int]] = None,
              dtype: str = "bfloat16", top_p: float = 1.0, min_p: float = 0.0,
              repetition_penalty: float = 1.0, repetition_window: int = 64,
-             max_batch: int = 8, max_context: Optional[int] = None, **engine_args) -> list[Output]:
+             max_batch: int = 8, max_context: Optional[int] = None, use_graphs: bool = True,
+             **engine_args) -> list[Output]:
     """One call from a model folder and token-id prompts to generated token ids."""
     from ..sampling.sampler import DeviceSampler
     from .step import Engine
@@ -160,4 +181,4 @@ def generate(model_dir: str, prompts: Sequence[Sequence[int]], max_tokens: int =
     params = SamplingParams(temperature, top_p, min_p, repetition_penalty, repetition_window, seed)
     if stop_ids is None:
         stop_ids = engine.spec.stop_token_ids
-    return Generator(engine, sampler).generate(prompts, max_tokens, params, stop_ids)
+    return Generator(engine, sampler, use_graphs).generate(prompts, max_tokens, params, stop_ids)

@@ -191,6 +191,11 @@ class Engine:
         return memory_plan(self.model, expected, self.dtype, self.max_tokens, self.max_slots,
                            self.max_context, self.page_size, self.chunk_tokens)
 
+    def decode_session(self, sampler, params=None):
+        """A `DecodeSession` over this engine (decode steps replayed as CUDA graphs)."""
+        from .graphs import DecodeSession
+        return DecodeSession(self, sampler, params)
+
     # ---- sequences ---------------------------------------------------------
     def acquire(self) -> int:
         return self.cache.acquire()

@@ -44,7 +44,12 @@ def _need_cuda(*tensors):
             raise KernelError("kernels run on CUDA tensors only; there is no CPU path")
 
 
-def _call(libname: str, fn: str, *args):
+LAUNCHES = 0      # kernel launches made through this module (a claim bench.py reports)
+
+
+def _call(libname: str, fn: str, *args, launches: int = 1):
+    global LAUNCHES
+    LAUNCHES += launches
     lib = _build.load(libname)
     rc = getattr(lib, fn)(*args)
     if rc != 0:
@@ -160,3 +165,10 @@ def sample(logits: torch.Tensor, uniforms: torch.Tensor, tokens: torch.Tensor, p
     _call("core", "mdma_sample", _ptr(logits), _i(n), _i(logits.shape[1]), _ptr(history),
           _ptr(history_len), _i(hstride), _ptr(uniforms), _f(temperature), _f(top_p), _f(min_p),
           _f(penalty), _i(penalty_window), _ptr(probs_scratch), _ptr(tokens), _ptr(flags), _stream())
+
+
+def advance_decode(tokens: torch.Tensor, ids: torch.Tensor, tok_pos: torch.Tensor, seq_pos0: torch.Tensor,
+                   n: int) -> None:
+    """ids <- tokens, positions += 1: what a decode step leaves for the next one."""
+    _need_cuda(tokens, ids, tok_pos, seq_pos0)
+    _call("core", "mdma_advance_decode", _ptr(tokens), _ptr(ids), _ptr(tok_pos), _ptr(seq_pos0), _i(n), _stream())

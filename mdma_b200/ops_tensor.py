@@ -77,4 +77,5 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
         reserve_scratch(a.device, need)
     _call("tensor", "mdma_gemm_tc", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), _ptr(out),
           _i(int(out.dtype == torch.float32)), _i(out.stride(0)), _i(M), _i(N), _i(K), _i(bn), _i(splits),
-          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]), _stream())
+          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]), _stream(),
+          launches=2 if splits > 1 else 1)

@@ -28,6 +28,7 @@ def ops_tensor_attention_ready() -> bool:
 
 @MIXERS.register("attention")
 class Attention(Part):
+    graph_safe = True      # forward reads no host-side per-step values
     def __init__(self, spec):
         super().__init__(spec)
         p = self.params

@@ -12,6 +12,7 @@ from .linear import Linear
 
 @FEED_FORWARDS.register("gated_mlp")
 class GatedMLP(Part):
+    graph_safe = True      # forward reads no host-side per-step values
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden = int(self.params["hidden_size"])

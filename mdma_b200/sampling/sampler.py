@@ -25,33 +25,43 @@ class DeviceSampler:
         self._probs: Optional[torch.Tensor] = None
         self._out_host = torch.empty(2 * max_rows, dtype=torch.int32).pin_memory()
 
-    def sample_device(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
-                      steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> None:
-        """Fill self.tokens[:n] and self.flags[:n] for the n rows of `logits`."""
-        n = logits.shape[0]
-        assert n <= self.max_rows and logits.shape[1] == self.vocab
-        if params.temperature <= 0.0 and (params.repetition_penalty == 1.0 or not histories):
-            ops.argmax(logits, self.tokens, self.flags, n)
-            return
+    def ensure_probs(self) -> None:
+        if self._probs is None:
+            self._probs = torch.empty(self.max_rows * self.vocab, dtype=torch.float32, device=self.device)
+
+    def stage_inputs(self, params: SamplingParams, requests, steps, histories=None) -> bool:
+        """Upload what the sampled path reads: one uniform number per row, keyed by
+        (seed, request, step), and the rows' recent tokens.  Returns whether histories are in use."""
+        n = len(requests)
         u = np.asarray([uniform(params.seed, r, s) for r, s in zip(requests, steps)], dtype=np.float32)
         self.uniforms[:n].copy_(torch.from_numpy(u))
-        hist = hlen = None
         if params.repetition_penalty != 1.0 and params.repetition_window > 0 and histories is not None:
             w = min(params.repetition_window, self.history_cap)
             rows = np.zeros((n, self.history_cap), dtype=np.int32)
             lens = np.zeros(n, dtype=np.int32)
             for i, h in enumerate(histories):
-                tail = list(h[-w:]) if w else []
+                tail = list(h[-w:])
                 rows[i, :len(tail)] = tail
                 lens[i] = len(tail)
             self.history[:n].copy_(torch.from_numpy(rows))
             self.history_len[:n].copy_(torch.from_numpy(lens))
-            hist, hlen = self.history, self.history_len
-        if self._probs is None or self._probs.numel() < n * self.vocab:
-            self._probs = torch.empty(self.max_rows * self.vocab, dtype=torch.float32, device=self.device)
+            return True
+        return False
+
+    def sample_device(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
+                      steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> None:
+        """Fill self.tokens[:n] and self.flags[:n] for the n rows of `logits`."""
+        n = logits.shape[0]
+        assert n <= self.max_rows and logits.shape[1] == self.vocab
+        penalised = params.repetition_penalty != 1.0 and params.repetition_window > 0 and histories is not None
+        if params.temperature <= 0.0 and not penalised:
+            ops.argmax(logits, self.tokens, self.flags, n)
+            return
+        use_hist = self.stage_inputs(params, requests, steps, histories)
+        self.ensure_probs()
         ops.sample(logits, self.uniforms, self.tokens, self._probs, params.temperature, params.top_p,
                    params.min_p, params.repetition_penalty, min(params.repetition_window, self.history_cap),
-                   hist, hlen, self.flags, n)
+                   self.history if use_hist else None, self.history_len if use_hist else None, self.flags, n)
 
     def sample(self, logits, params, requests, steps, histories=None) -> tuple[list[int], list[int]]:
         n = logits.shape[0]
