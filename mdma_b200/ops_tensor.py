@@ -79,3 +79,41 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
           _i(int(out.dtype == torch.float32)), _i(out.stride(0)), _i(M), _i(N), _i(K), _i(bn), _i(splits),
           _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]), _stream(),
           launches=2 if splits > 1 else 1)
+
+
+def attention_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    return (n_kv_heads > 0 and n_heads % n_kv_heads == 0 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+            and n_heads // n_kv_heads <= 64)
+
+
+def attention_splits(n_seqs: int, max_new: int, max_len: int, n_heads: int, n_kv_heads: int, sms: int) -> int:
+    """How many ways to divide a tile's keys so that the grid fills the device."""
+    tile_tokens = max(1, 64 // (n_heads // n_kv_heads))
+    blocks = -(-max_new // tile_tokens) * n_seqs * n_kv_heads
+    if blocks >= 2 * sms:
+        return 1
+    key_blocks = max(1, -(-max_len // 64))
+    return max(1, min(-(-2 * sms // blocks), key_blocks, 32))
+
+
+def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+              window: int, scale: float, splits: Optional[int] = None) -> None:
+    """Causal grouped-query attention of the step's tokens over the paged cache (bfloat16)."""
+    _need_cuda(qkv, view.k, view.v, out, view.page_table)
+    if qkv.dtype != torch.bfloat16 or view.k.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention takes bfloat16")
+    assert qkv.stride(1) == 1 and out.is_contiguous() and out.shape[1] == n_heads * head_dim
+    st = _device_state(qkv.device)
+    if splits is None:
+        splits = attention_splits(ctx.n_seqs, ctx.max_new, ctx.max_len, n_heads, n_kv_heads, st["sms"])
+    need = ctx.n_tokens * n_heads * splits * (head_dim + 2) if splits > 1 else 0
+    if need > st["scratch"].numel():
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("attention scratch is too small and cannot grow during graph capture")
+        reserve_scratch(qkv.device, need)
+    _call("tensor", "mdma_attention_mma", _ptr(qkv), _i(qkv.stride(0)), _ptr(view.k), _ptr(view.v),
+          _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
+          _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs),
+          _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale), _i(splits),
+          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _stream(),
+          launches=2 if splits > 1 else 1)

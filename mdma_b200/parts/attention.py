@@ -21,11 +21,6 @@ from .base import Part
 from .linear import Linear
 
 
-def ops_tensor_attention_ready() -> bool:
-    from .. import ops_tensor
-    return hasattr(ops_tensor, "attention")
-
-
 @MIXERS.register("attention")
 class Attention(Part):
     graph_safe = True      # forward reads no host-side per-step values
@@ -76,6 +71,10 @@ class Attention(Part):
             # one product for q, k and v: rows [q heads | k heads | v heads]
             fused = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
                                tensors["v_proj.weight"]], dim=0).contiguous()
+        self._fast_ok = False
+        if rt.attention == "fast":
+            from .. import ops_tensor
+            self._fast_ok = ops_tensor.attention_supported(self.n_heads, self.n_kv_heads, self.head_dim)
         self.qkv_proj = Linear(fused, rt)
         self.o_proj = Linear(tensors["o_proj.weight"], rt)
 
@@ -86,7 +85,7 @@ class Attention(Part):
         self.qkv_proj.store(h, qkv, n)
         write = owns_cache and not self.shared_cache
         self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, view, write)
-        if self.rt.attention == "fast" and ops_tensor_attention_ready():
+        if self.rt.attention == "fast" and self._fast_ok:
             from .. import ops_tensor
             ops_tensor.attention(ctx, qkv, view, out, self.n_heads, self.n_kv_heads, self.head_dim,
                                  self.window, self.scale)

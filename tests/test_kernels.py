@@ -185,6 +185,80 @@ def test_attention_finds_one_far_key():
     close(out, want, 2e-5)
 
 
+class StepMeta:
+    """Sequences with `new` tokens each on top of `cached` tokens already in the cache."""
+
+    def __init__(self, cached, new):
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        starts = [0]
+        for n in new:
+            starts.append(starts[-1] + n)
+        self.n_seqs, self.n_tokens = len(new), starts[-1]
+        self.max_new, self.max_len = max(new), max(c + n for c, n in zip(cached, new))
+        self.seq_start, self.seq_pos0, self.seq_slot = i32(starts), i32(cached), i32(list(range(len(new))))
+        self.tok_seq = [s for s, n in enumerate(new) for _ in range(n)]
+        self.tok_pos = [c + j for c, n in zip(cached, new) for j in range(n)]
+
+
+@pytest.mark.parametrize("H,K,hd,window", [(8, 2, 128, 0), (6, 2, 48, 0), (4, 4, 16, 0), (12, 2, 64, 0),
+                                           (6, 1, 80, 0), (8, 2, 128, 100), (5, 5, 112, 33), (32, 8, 128, 0)])
+@pytest.mark.parametrize("case", ["prefill", "chunked", "decode", "decode_split"])
+def test_attention_tensor(H, K, hd, window, case):
+    """The tensor-core attention against the float64 statement of the reference's loop:
+    whole prompts, prompts on top of a cached prefix, single tokens, and keys split over blocks."""
+    from mdma_b200 import ops_tensor
+    torch.manual_seed(H * 1000 + hd)
+    page = 64
+    if case == "prefill":
+        cached, new = [0, 0, 0], [150, 3, 65]
+    elif case == "chunked":
+        cached, new = [70, 129, 1], [100, 20, 64]
+    else:
+        cached, new = [299, 0, 64, 1000], [1, 1, 1, 1]
+    lens = [c + n for c, n in zip(cached, new)]
+    kc, vc, table, max_pages, dense = fill_cache(lens, K, hd, page, torch.bfloat16, seed=hd)
+    meta = StepMeta(cached, new)
+    T = meta.n_tokens
+    q = (torch.randn(T, (H + 2 * K) * hd, device=DEV)).bfloat16()
+    out = torch.full((T + 1, H * hd), 9.0, device=DEV, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+
+    class View:
+        pass
+    view = View()
+    view.k, view.v, view.page_table, view.max_pages, view.page_size = kc, vc, table, max_pages, page
+    splits = {"decode_split": 5, "chunked": 2}.get(case)
+    ops_tensor.attention(meta, q, view, out, H, K, hd, window, scale, splits=splits)
+    want = reference_attention(q[:, :H * hd].double().cpu().reshape(T, H, hd), dense, meta.tok_seq, meta.tok_pos,
+                               scale, window)
+    close(out[:T], want, 2e-2, 2e-2)
+    assert bool((out[T:] == 9.0).all())
+
+
+def test_attention_tensor_finds_one_far_key_and_the_window_edge():
+    from mdma_b200 import ops_tensor
+    H, K, hd, page = 4, 1, 64, 64
+    kc, vc, table, max_pages, dense = fill_cache([900], K, hd, page, torch.bfloat16, seed=5)
+    k, v = dense[0]
+    q = torch.randn(1, H * hd).bfloat16()
+    for target, window, seen in ((123, 0, True), (899 - 99, 100, True), (899 - 100, 100, False)):
+        kk = k.clone()
+        kk[target, 0] = (q[0, :hd].float() * 3.0).bfloat16()          # head 0 points at one key
+        pg = int(table[0, target // page])
+        kc2 = kc.clone()
+        kc2[pg, target % page, 0] = kk[target, 0].to(DEV)
+        meta = StepMeta([899], [1])
+        out = torch.zeros(1, H * hd, device=DEV, dtype=torch.bfloat16)
+
+        class View:
+            pass
+        view = View()
+        view.k, view.v, view.page_table, view.max_pages, view.page_size = kc2, vc, table, max_pages, page
+        ops_tensor.attention(meta, q.to(DEV), view, out, H, K, hd, window, 1.0, splits=3)
+        hit = (out[0, :hd].float().cpu() - v[target, 0].float()).abs().max().item() < 0.05
+        assert hit == seen, (target, window)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 5, 3), (67, 130, 100), (5, 331, 120), (200, 64, 17)])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_gemm_simt(M, N, K, dt):
