@@ -1,271 +1,5 @@
-// Causal grouped-query attention over the paged cache on the tensor cores
-// (bfloat16 in, float softmax and accumulation), for prefill and for decode.
-//
-// A block works on one tile of query rows of one kv head of one sequence.  The
-// rows of a tile are (token, query head of the group) pairs, token-major, so
-// the G query heads that share a kv head share its key and value loads: a
-// prefill tile holds 64/G tokens, a decode tile one token.  Keys and values
-// stream through shared memory in blocks of 64 (double-buffered cp.async,
-// looked up page by page), scores and the running maximum and sum stay in
-// registers in float, probabilities are rounded to bfloat16 for the P*V
-// product, as is usual.  With `splits` > 1 the key blocks of a tile are divided
-// among that many blocks of the grid; each writes its unnormalised output with
-// its maximum and sum, and a second kernel merges them in split order, so the
-// result does not depend on timing.
-// Limits: head_dim a multiple of 16 up to 128; group size up to 64.
-#include "common.cuh"
-
-namespace mdma {
-
-constexpr int kRows = 64;        // query rows per block (4 warps x 16)
-constexpr int kKeys = 64;        // keys per block of the stream
-constexpr int kAttnThreads = 128;
-
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
-    const int bytes = valid ? 16 : 0;       // 0: the 16 bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                          uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-struct AttnParams {
-    const __nv_bfloat16* q; int q_stride;          // rows of the fused projection; queries first
-    const __nv_bfloat16* k_cache; const __nv_bfloat16* v_cache;   // [pages, page_size, kv_heads, head_dim]
-    const int* seq_start; const int* seq_pos0; const int* seq_slot;
-    const int* page_table; int max_pages; int page_size;
-    __nv_bfloat16* out;                             // [tokens, heads * head_dim]
-    float* part_o; float* part_ml;                  // split partials: [tokens, heads, splits, head_dim], [.., 2]
-    int n_heads, n_kv_heads, head_dim, group, tile_tokens, window, splits;
-    float scale_log2;                               // scale * log2(e)
-};
-
-// Tile shared-memory rows are DMAX elements wide; 16-byte chunk c of row r sits at chunk c ^ (r & 7).
-template <int DMAX>
-__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
-    return (uint32_t)(row * DMAX * 2 + ((chunk ^ (row & 7)) << 4));
-}
-
-template <int DMAX>
-__global__ void __launch_bounds__(kAttnThreads)
-attention_mma_kernel(const AttnParams p) {
-    constexpr int kChunks = DMAX / 8;              // 16-byte chunks per row
-    constexpr int kTile = kRows * DMAX * 2;        // bytes of one 64-row tile
-    extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t sK = sQ + kTile, sV = sK + 2 * kTile;
-
-    const int seq = blockIdx.y;
-    const int kvh = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
-    const int row0_seq = p.seq_start[seq];
-    const int n_new = p.seq_start[seq + 1] - row0_seq;
-    const int tok0 = blockIdx.x * p.tile_tokens;            // first token of this tile within the sequence's new tokens
-    if (tok0 >= n_new) return;
-    const int n_tok = min(p.tile_tokens, n_new - tok0);
-    const int pos0 = p.seq_pos0[seq] + tok0;                // position of the tile's first token
-    const int last_pos = pos0 + n_tok - 1;
-    const int* pages = p.page_table + (size_t)p.seq_slot[seq] * p.max_pages;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int D = p.head_dim, G = p.group;
-    const int d_chunks = D / 8;
-
-    // key range of the tile, then of this split
-    const int first_key = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;
-    const int blk_lo = first_key / kKeys, blk_hi = last_pos / kKeys + 1;
-    const int per = (blk_hi - blk_lo + p.splits - 1) / p.splits;
-    const int b0 = blk_lo + split * per, b1 = min(blk_hi, b0 + per);
-
-    // ---- Q tile -> shared -------------------------------------------------
-    for (int i = threadIdx.x; i < kRows * kChunks; i += kAttnThreads) {
-        const int r = i / kChunks, c = i % kChunks;
-        const int t = r / G, g = r % G;
-        const bool valid = t < n_tok && c < d_chunks;
-        const __nv_bfloat16* src = p.q + (size_t)(row0_seq + tok0 + (valid ? t : 0)) * p.q_stride +
-                                   (size_t)(kvh * G + g) * D + (valid ? c : 0) * 8;
-        cp_async_16(sQ + tile_offset<DMAX>(r, c), src, valid);
-    }
-    auto load_kv = [&](int blk, int stage) {
-        for (int i = threadIdx.x; i < kKeys * kChunks; i += kAttnThreads) {
-            const int r = i / kChunks, c = i % kChunks;
-            const int key = blk * kKeys + r;
-            const bool valid = key <= last_pos && c < d_chunks;
-            size_t off = 0;
-            if (valid) {
-                const int page = pages[key / p.page_size];
-                off = (((size_t)page * p.page_size + key % p.page_size) * p.n_kv_heads + kvh) * D + c * 8;
-            }
-            cp_async_16(sK + stage * kTile + tile_offset<DMAX>(r, c), p.k_cache + off, valid);
-            cp_async_16(sV + stage * kTile + tile_offset<DMAX>(r, c), p.v_cache + off, valid);
-        }
-    };
-    if (b0 < b1) load_kv(b0, 0);
-    cp_async_commit();
-
-    // per-thread rows: r_lo = warp*16 + lane/4, r_hi = r_lo + 8
-    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
-    const int pos_lo = pos0 + min(r_lo / G, n_tok - 1), pos_hi = pos0 + min(r_hi / G, n_tok - 1);
-    const int win_lo = p.window > 0 ? pos_lo + 1 - p.window : 0, win_hi = p.window > 0 ? pos_hi + 1 - p.window : 0;
-
-    float o[DMAX / 8][4];
-#pragma unroll
-    for (int n = 0; n < DMAX / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-
-    for (int blk = b0; blk < b1; ++blk) {
-        const int stage = (blk - b0) & 1;
-        if (blk + 1 < b1) load_kv(blk + 1, stage ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-
-        // ---- S = Q K^T for this warp's 16 rows x 64 keys ---------------------
-        float s[kKeys / 8][4];
-#pragma unroll
-        for (int n = 0; n < kKeys / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
-#pragma unroll
-        for (int kd = 0; kd < DMAX / 16; ++kd) {
-            if (kd * 16 < D) {
-                uint32_t a0, a1, a2, a3;
-                ldmatrix_x4(sQ + tile_offset<DMAX>(warp * 16 + (lane & 15), kd * 2 + (lane >> 4)), a0, a1, a2, a3);
-#pragma unroll
-                for (int n2 = 0; n2 < kKeys / 16; ++n2) {
-                    uint32_t k0, k1, k2, k3;
-                    // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
-                    const int krow = n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
-                    ldmatrix_x4(sK + stage * kTile + tile_offset<DMAX>(krow, kd * 2 + ((lane >> 3) & 1)), k0, k1, k2, k3);
-                    mma_16816(s[n2 * 2], a0, a1, a2, a3, k0, k1);
-                    mma_16816(s[n2 * 2 + 1], a0, a1, a2, a3, k2, k3);
-                }
-            }
-        }
-        // ---- mask, online softmax ---------------------------------------------
-        const int key_base = blk * kKeys + (lane & 3) * 2;
-        float mx_lo = m_lo, mx_hi = m_hi;
-#pragma unroll
-        for (int n = 0; n < kKeys / 8; ++n) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = key_base + n * 8 + e;
-                const float v_lo = (key <= pos_lo && key >= win_lo) ? s[n][e] * p.scale_log2 : -INFINITY;
-                const float v_hi = (key <= pos_hi && key >= win_hi) ? s[n][2 + e] * p.scale_log2 : -INFINITY;
-                s[n][e] = v_lo; s[n][2 + e] = v_hi;
-                mx_lo = fmaxf(mx_lo, v_lo); mx_hi = fmaxf(mx_hi, v_hi);
-            }
-        }
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        // a row with no visible key yet keeps m = -inf; use 0 as its reference so that exp2(-inf - 0) = 0
-        const float ref_lo = mx_lo == -INFINITY ? 0.f : mx_lo, ref_hi = mx_hi == -INFINITY ? 0.f : mx_hi;
-        const float corr_lo = exp2f(m_lo - ref_lo), corr_hi = exp2f(m_hi - ref_hi);
-        m_lo = mx_lo; m_hi = mx_hi;
-        float sum_lo = 0.f, sum_hi = 0.f;
-        uint32_t pa[kKeys / 16][4];
-#pragma unroll
-        for (int n = 0; n < kKeys / 8; ++n) {
-            const float p0 = exp2f(s[n][0] - ref_lo), p1 = exp2f(s[n][1] - ref_lo);
-            const float p2 = exp2f(s[n][2] - ref_hi), p3 = exp2f(s[n][3] - ref_hi);
-            sum_lo += p0 + p1; sum_hi += p2 + p3;
-            pa[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
-            pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
-        }
-        l_lo = l_lo * corr_lo + sum_lo; l_hi = l_hi * corr_hi + sum_hi;
-#pragma unroll
-        for (int n = 0; n < DMAX / 8; ++n) {
-            o[n][0] *= corr_lo; o[n][1] *= corr_lo; o[n][2] *= corr_hi; o[n][3] *= corr_hi;
-        }
-        // ---- O += P V -----------------------------------------------------------
-#pragma unroll
-        for (int kk = 0; kk < kKeys / 16; ++kk) {
-#pragma unroll
-            for (int n2 = 0; n2 < DMAX / 16; ++n2) {
-                if (n2 * 16 < D) {
-                    uint32_t v0, v1, v2, v3;
-                    // transposed loads: (keys lo, d lo), (keys hi, d lo), (keys lo, d hi), (keys hi, d hi)
-                    const int vrow = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-                    ldmatrix_x4_trans(sV + stage * kTile + tile_offset<DMAX>(vrow, n2 * 2 + (lane >> 4)), v0, v1, v2, v3);
-                    mma_16816(o[n2 * 2], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], v0, v1);
-                    mma_16816(o[n2 * 2 + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], v2, v3);
-                }
-            }
-        }
-        __syncthreads();        // the stage may be overwritten by the next iteration's loads
-    }
-    cp_async_wait<0>();
-
-    // ---- finish: row sums across the quad, then write ----------------------------
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int r = half ? r_hi : r_lo;
-        const int t = r / G, g = r % G;
-        if (t >= n_tok) continue;
-        const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
-        const size_t token = (size_t)(row0_seq + tok0 + t);
-        const int head = kvh * G + g;
-        if (p.splits == 1) {
-            const float inv = 1.0f / l;
-            __nv_bfloat16* dst = p.out + (token * p.n_heads + head) * D;
-#pragma unroll
-            for (int n = 0; n < DMAX / 8; ++n) {
-                const int d = n * 8 + (lane & 3) * 2;
-                if (d < D)
-                    *reinterpret_cast<__nv_bfloat162*>(dst + d) =
-                        __floats2bfloat162_rn(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
-            }
-        } else {
-            const size_t slot = (token * p.n_heads + head) * p.splits + split;
-            float* dst = p.part_o + slot * D;
-#pragma unroll
-            for (int n = 0; n < DMAX / 8; ++n) {
-                const int d = n * 8 + (lane & 3) * 2;
-                if (d < D) { dst[d] = o[n][half * 2]; dst[d + 1] = o[n][half * 2 + 1]; }
-            }
-            if ((lane & 3) == 0) { p.part_ml[slot * 2] = m; p.part_ml[slot * 2 + 1] = l; }
-        }
-    }
-}
-
-// out[token, head, :] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, splits taken in order.
-__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       __nv_bfloat16* __restrict__ out, int splits, int head_dim) {
-    const size_t th = blockIdx.x;                   // token * heads + head
-    const float* ml = part_ml + th * splits * 2;
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[s * 2]);
-    float l = 0.f;
-    for (int s = 0; s < splits; ++s) if (ml[s * 2] != -INFINITY) l += exp2f(ml[s * 2] - m) * ml[s * 2 + 1];
-    const float inv = 1.0f / l;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < splits; ++s)
-            if (ml[s * 2] != -INFINITY) acc += exp2f(ml[s * 2] - m) * part_o[(th * splits + s) * head_dim + d];
-        out[th * head_dim + d] = __float2bfloat16_rn(acc * inv);
-    }
-}
-
-}  // namespace mdma
+// C entry points of the tensor-core attention (kernels in attention_mma.cuh).
+#include "attention_mma.cuh"
 
 using namespace mdma;
 
@@ -273,14 +7,12 @@ extern "C" {
 
 // Whether the tensor-core attention takes this geometry.
 int mdma_attention_mma_supported(int n_heads, int n_kv_heads, int head_dim) {
-    if (n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
-    const int g = n_heads / n_kv_heads;
-    return (head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128 && g <= kRows) ? 1 : 0;
+    return attention_mma_supported(n_heads, n_kv_heads, head_dim);
 }
 
 // Floats of scratch a call needs: n_tokens * n_heads * splits * (head_dim + 2); 0 for splits == 1.
 long mdma_attention_mma_scratch(int n_tokens, int n_heads, int head_dim, int splits) {
-    return splits > 1 ? (long)n_tokens * n_heads * splits * (head_dim + 2) : 0;
+    return attention_mma_scratch_floats(n_tokens, n_heads, head_dim, splits);
 }
 
 int mdma_attention_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache,
@@ -288,48 +20,9 @@ int mdma_attention_mma(const void* q, int q_stride, const void* k_cache, const v
                        int max_pages, int page_size, void* out, int n_tokens, int n_seqs, int max_new,
                        int n_heads, int n_kv_heads, int head_dim, int window, float scale, int splits,
                        float* scratch, long scratch_floats, cudaStream_t stream) {
-    MDMA_REQUIRE(mdma_attention_mma_supported(n_heads, n_kv_heads, head_dim),
-                 "attention_mma: heads %d / kv heads %d / head_dim %d is outside its limits (head_dim a multiple of 16 up to 128, group up to 64)",
-                 n_heads, n_kv_heads, head_dim);
-    MDMA_REQUIRE(page_table && page_size > 0 && max_pages > 0 && window >= 0, "attention_mma: bad cache geometry");
-    MDMA_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0, "attention_mma: query rows must be 16-byte aligned");
-    MDMA_REQUIRE(n_seqs <= 65535 && (long)n_kv_heads * splits <= 65535, "attention_mma: grid too large");
-    if (n_tokens == 0 || n_seqs == 0) return 0;
-    if (splits < 1) splits = 1;
-    AttnParams p;
-    p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
-    p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
-    p.seq_start = seq_start; p.seq_pos0 = seq_pos0; p.seq_slot = seq_slot;
-    p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size;
-    p.out = (__nv_bfloat16*)out;
-    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
-    p.group = n_heads / n_kv_heads; p.tile_tokens = kRows / p.group; p.window = window; p.splits = splits;
-    p.scale_log2 = scale * 1.4426950408889634f;
-    p.part_o = nullptr; p.part_ml = nullptr;
-    if (splits > 1) {
-        const long need = mdma_attention_mma_scratch(n_tokens, n_heads, head_dim, splits);
-        MDMA_REQUIRE(scratch && scratch_floats >= need, "attention_mma: %d splits need %ld floats of scratch, %ld given", splits, need, scratch_floats);
-        p.part_o = scratch;
-        p.part_ml = scratch + (long)n_tokens * n_heads * splits * head_dim;
-    }
-    dim3 grid((max_new + p.tile_tokens - 1) / p.tile_tokens, n_seqs, n_kv_heads * splits);
-    if (head_dim <= 64) {
-        constexpr int bytes = 5 * kRows * 64 * 2;
-        static bool once = false;
-        if (!once) { cudaFuncSetAttribute(attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
-        attention_mma_kernel<64><<<grid, kAttnThreads, bytes, stream>>>(p);
-    } else {
-        constexpr int bytes = 5 * kRows * 128 * 2;
-        static bool once = false;
-        if (!once) { cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
-        attention_mma_kernel<128><<<grid, kAttnThreads, bytes, stream>>>(p);
-    }
-    MDMA_LAUNCH_OK("attention_mma");
-    if (splits > 1) {
-        attention_merge_kernel<<<n_tokens * n_heads, 64, 0, stream>>>(p.part_o, p.part_ml, p.out, splits, head_dim);
-        MDMA_LAUNCH_OK("attention_merge");
-    }
-    return 0;
+    return launch_attention_mma(q, q_stride, k_cache, v_cache, seq_start, seq_pos0, seq_slot, page_table,
+                                max_pages, page_size, out, n_tokens, n_seqs, max_new, n_heads, n_kv_heads,
+                                head_dim, window, scale, splits, scratch, scratch_floats, stream);
 }
 
 }  // extern "C"

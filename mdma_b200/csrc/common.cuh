@@ -14,11 +14,11 @@ enum DType : int { kF32 = 0, kBF16 = 1 };
 
 // The last error of this library, as text.  Every exported function returns 0
 // on success and non-zero after storing a message here.
-inline char* error_buffer() {
+static inline char* error_buffer() {
     static char buf[1024] = {0};
     return buf;
 }
-inline int fail(const char* fmt, ...) {
+static inline int fail(const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
     vsnprintf(error_buffer(), 1024, fmt, ap);
