@@ -25,19 +25,55 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
 // ---------------------------------------------------------------- RMSNorm
 // y = x * rsqrt(mean(x^2) + eps) * w, one block per row.  `rows` (optional)
 // picks which rows of x are normed: y[i] = norm(x[rows[i]]).
-template <typename TO, typename TW>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
-                               const int* __restrict__ rows, TO* __restrict__ y, int width, float eps) {
+// With `splits` > 0 the row is first completed: x += sum_s partial[s] (the
+// K-split partial sums of the matrix product that feeds the residual stream,
+// added in split order) and written back, so the product's reduction, the
+// residual add and the norm are one pass over the row.
+// PER > 0: each thread keeps PER elements of the row in registers (one read of
+// x); PER == 0: rows of any width, read twice.
+template <typename TO, typename TW, int PER>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ partial, int splits,
+                               size_t split_stride, const TW* __restrict__ w, const int* __restrict__ rows,
+                               TO* __restrict__ y, int width, float eps) {
     __shared__ float scratch[32];
     const int r = blockIdx.x;
-    const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
-    float ss = 0.f;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) { const float v = xr[e]; ss += v * v; }
-    ss = block_sum(ss, scratch);
-    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    const size_t src = (size_t)(rows ? rows[r] : r) * width;
+    float* xr = x + src;
     TO* yr = y + (size_t)r * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x)
-        yr[e] = from_float<TO>(xr[e] * scale * to_float(w[e]));
+    float ss = 0.f;
+    if (PER > 0) {
+        float v[PER > 0 ? PER : 1];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            float a = 0.f;
+            if (e < width) {
+                a = xr[e];
+                for (int sidx = 0; sidx < splits; ++sidx) a += partial[(size_t)sidx * split_stride + src + e];
+                if (splits > 0) xr[e] = a;
+            }
+            v[i] = a;
+            ss += a * a;
+        }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < width) yr[e] = from_float<TO>(v[i] * scale * to_float(w[e]));
+        }
+    } else {
+        for (int e = threadIdx.x; e < width; e += blockDim.x) {
+            float a = xr[e];
+            for (int sidx = 0; sidx < splits; ++sidx) a += partial[(size_t)sidx * split_stride + src + e];
+            if (splits > 0) xr[e] = a;
+            ss += a * a;
+        }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+        for (int e = threadIdx.x; e < width; e += blockDim.x)
+            yr[e] = from_float<TO>(xr[e] * scale * to_float(w[e]));
+    }
 }
 
 // ------------------------------------------------- rotary + cache write
@@ -45,8 +81,13 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
 // [q heads | k heads | v heads].  q is rotated in place; rotated k and raw v go
 // to the cache row of (slot, position): page page_table[slot][pos / page_size],
 // row pos % page_size of that page.
+// With `splits` > 0 the projection row is read as the sum of that many float
+// partial rows (the K-split partial sums of the projection, in split order)
+// instead of from qkv; the rotated queries are still written to qkv.
 template <typename T>
 __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
+                                        const float* __restrict__ partial, int splits, size_t split_stride,
+                                        int partial_width,
                                         const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                         const int* __restrict__ seq_slot,
                                         const float* __restrict__ inv_freq,
@@ -59,6 +100,13 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
     const int pos = tok_pos[t];
     T* src = qkv + (size_t)t * row_stride + (size_t)h * head_dim;
     T* dst = src;
+    const float* psrc = partial + (size_t)t * partial_width + (size_t)h * head_dim;
+    auto load = [&](int d) -> float {
+        if (splits == 0) return to_float(src[d]);
+        float a = 0.f;
+        for (int sidx = 0; sidx < splits; ++sidx) a += psrc[(size_t)sidx * split_stride + d];
+        return a;
+    };
     bool rotate = true;
     if (h >= n_heads) {
         if (!write_kv) return;
@@ -78,14 +126,14 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
             const float a = (float)pos * inv_freq[i];
             float s, c;
             sincosf(a, &s, &c);
-            const float x0 = to_float(src[d0]), x1 = to_float(src[d1]);
+            const float x0 = load(d0), x1 = load(d1);
             dst[d0] = from_float<T>(x0 * c - x1 * s);
             dst[d1] = from_float<T>(x0 * s + x1 * c);
         }
-        if (dst != src)
-            for (int d = rotary_dim + threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = src[d];
+        if (dst != src || splits > 0)
+            for (int d = rotary_dim + threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = from_float<T>(load(d));
     } else {
-        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = src[d];
+        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = from_float<T>(load(d));
     }
 }
 
@@ -107,6 +155,20 @@ __global__ void advance_decode_kernel(const int* __restrict__ tokens, int* __res
     ids[i] = tokens[i];
     tok_pos[i] += 1;
     seq_pos0[i] += 1;
+}
+
+template <typename TO, typename TW>
+static void launch_rmsnorm(float* x, const float* partial, int splits, size_t split_stride, const TW* w,
+                           const int* rows, TO* y, int n_rows, int width, float eps, cudaStream_t stream) {
+    auto threads_for = [&](int per) { int t = ((width + per - 1) / per + 31) / 32 * 32; return t < 64 ? 64 : t; };
+    if (width <= 4096)
+        rmsnorm_kernel<TO, TW, 4><<<n_rows, threads_for(4), 0, stream>>>(x, partial, splits, split_stride, w, rows, y, width, eps);
+    else if (width <= 8192)
+        rmsnorm_kernel<TO, TW, 8><<<n_rows, threads_for(8), 0, stream>>>(x, partial, splits, split_stride, w, rows, y, width, eps);
+    else if (width <= 16384)
+        rmsnorm_kernel<TO, TW, 16><<<n_rows, threads_for(16), 0, stream>>>(x, partial, splits, split_stride, w, rows, y, width, eps);
+    else
+        rmsnorm_kernel<TO, TW, 0><<<n_rows, 1024, 0, stream>>>(x, partial, splits, split_stride, w, rows, y, width, eps);
 }
 
 }  // namespace mdma
@@ -134,19 +196,23 @@ int mdma_embed_rows(const void* table, int table_dtype, const int* ids, float* o
     return 0;
 }
 
-int mdma_rmsnorm(const float* x, const void* w, int w_dtype, const int* rows, void* y, int y_dtype,
-                 int n_rows, int width, float eps, cudaStream_t stream) {
+// partial/splits: optional K-split partial sums [splits, rows_total, width] to add into x first
+// (not with `rows`).
+int mdma_rmsnorm(float* x, const void* w, int w_dtype, const int* rows, void* y, int y_dtype,
+                 int n_rows, int width, float eps, const float* partial, int splits, long split_stride,
+                 cudaStream_t stream) {
     MDMA_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes");
+    MDMA_REQUIRE(splits >= 0 && (splits == 0 || (partial && !rows)), "rmsnorm: partial sums need a pointer and no row list");
     if (n_rows == 0) return 0;
-    const int threads = width >= 4096 ? 512 : 256;
     MDMA_DISPATCH_DTYPE(y_dtype, TO,
         MDMA_DISPATCH_DTYPE(w_dtype, TW,
-            rmsnorm_kernel<TO, TW><<<n_rows, threads, 0, stream>>>(x, (const TW*)w, rows, (TO*)y, width, eps)));
+            launch_rmsnorm<TO, TW>(x, partial, splits, (size_t)split_stride, (const TW*)w, rows, (TO*)y, n_rows, width, eps, stream)));
     MDMA_LAUNCH_OK("rmsnorm");
     return 0;
 }
 
-int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const int* tok_seq, const int* tok_pos,
+int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const float* partial, int splits,
+                          long split_stride, int partial_width, const int* tok_seq, const int* tok_pos,
                           const int* seq_slot, const float* inv_freq, void* k_cache, void* v_cache,
                           const int* page_table, int max_pages, int page_size,
                           int n_tokens, int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
@@ -154,6 +220,7 @@ int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const int* tok_s
     MDMA_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads >= 0 && head_dim > 0, "rope_cache_write: bad sizes");
     MDMA_REQUIRE(rotary_dim % 2 == 0 && rotary_dim <= head_dim, "rope_cache_write: rotary_dim %d does not fit head_dim %d", rotary_dim, head_dim);
     MDMA_REQUIRE(!write_kv || (page_table && page_size > 0 && max_pages > 0), "rope_cache_write: no cache pages");
+    MDMA_REQUIRE(splits >= 0 && (splits == 0 || partial), "rope_cache_write: partial sums need a pointer");
     if (n_tokens == 0) return 0;
     const int heads = n_heads + (write_kv ? 2 * n_kv_heads : 0);
     dim3 grid(n_tokens, heads);
@@ -161,7 +228,8 @@ int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const int* tok_s
     while (threads < head_dim / 2 && threads < 128) threads *= 2;
     MDMA_DISPATCH_DTYPE(dtype, T,
         rope_cache_write_kernel<T><<<grid, threads, 0, stream>>>(
-            (T*)qkv, row_stride, tok_seq, tok_pos, seq_slot, inv_freq, (T*)k_cache, (T*)v_cache,
+            (T*)qkv, row_stride, partial, splits, (size_t)split_stride, partial_width,
+            tok_seq, tok_pos, seq_slot, inv_freq, (T*)k_cache, (T*)v_cache,
             page_table, max_pages, page_size, n_heads, n_kv_heads, head_dim, rotary_dim, interleaved, write_kv));
     MDMA_LAUNCH_OK("rope_cache_write");
     return 0;

@@ -325,9 +325,29 @@ int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_coun
     return 0;
 }
 
+// Sums the partial results of a K split into `out` (mode store) or adds them to it (mode accumulate),
+// in split order.
+int mdma_splitk_reduce(int mode, const float* partial, int splits, int n_tokens, int n_features, void* out,
+                       int ldo, int out_f32, cudaStream_t stream) {
+    MDMA_REQUIRE(splits >= 1 && partial && out, "splitk_reduce: nothing to reduce");
+    MDMA_REQUIRE(mode == kTcStore || mode == kTcAccumulate, "splitk_reduce: unknown mode %d", mode);
+    const size_t total = (size_t)n_tokens * n_features;
+    if (total == 0) return 0;
+    const int blocks = (int)((total + 255) / 256);
+    if (mode == kTcAccumulate)
+        splitk_reduce_kernel<kTcAccumulate><<<blocks, 256, 0, stream>>>(partial, splits, n_tokens, n_features, out, ldo, out_f32);
+    else
+        splitk_reduce_kernel<kTcStore><<<blocks, 256, 0, stream>>>(partial, splits, n_tokens, n_features, out, ldo, out_f32);
+    MDMA_LAUNCH_OK("splitk_reduce");
+    return 0;
+}
+
+// `defer_reduce`: with a K split, leave the partial sums [splits, n_tokens, n_features] in `scratch`
+// for the caller's next kernel to add up; `splits_used` reports how many there are (1: `out` is complete).
 int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2, void* out, int out_f32,
                  int ldo, int n_tokens, int n_features, int K, int bn, int splits, float* scratch,
-                 long scratch_floats, int* status, cudaStream_t stream) {
+                 long scratch_floats, int* status, int defer_reduce, int* splits_used, cudaStream_t stream) {
+    if (splits_used) *splits_used = 1;
     MDMA_REQUIRE(n_tokens >= 0 && n_features > 0 && K > 0, "gemm_tc: bad sizes");
     MDMA_REQUIRE(K % 8 == 0, "gemm_tc: K=%d is not a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
     MDMA_REQUIRE(ldx % 8 == 0 && ldx >= K, "gemm_tc: activation pitch %d must be a multiple of 8 and at least K", ldx);
@@ -357,14 +377,9 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     MDMA_REQUIRE(scratch && scratch_floats >= need, "gemm_tc: a %d-way K split needs %ld floats of scratch, %ld given", splits, need, scratch_floats);
     p.partial = scratch;
     if (int rc = run_tc_bn<kTcPartial>(bn, x, ldx, w, w2, K, p, splits, stream)) return rc;
-    const size_t total = (size_t)n_tokens * n_features;
-    const int blocks = (int)((total + 255) / 256);
-    if (mode == kTcAccumulate)
-        splitk_reduce_kernel<kTcAccumulate><<<blocks, 256, 0, stream>>>(scratch, splits, n_tokens, n_features, out, ldo, out_f32);
-    else
-        splitk_reduce_kernel<kTcStore><<<blocks, 256, 0, stream>>>(scratch, splits, n_tokens, n_features, out, ldo, out_f32);
-    MDMA_LAUNCH_OK("splitk_reduce");
-    return 0;
+    if (splits_used) *splits_used = splits;
+    if (defer_reduce) return 0;
+    return mdma_splitk_reduce(mode, scratch, splits, n_tokens, n_features, out, ldo, out_f32, stream);
 }
 
 }  // extern "C"

@@ -37,25 +37,62 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* scratch) {
 }
 
 // tokens[r] = argmax(logits[r,:]); flags[r] = 1 if a logit of the row is not finite.
-__global__ void __launch_bounds__(kSampleThreads)
-argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ tokens, int* __restrict__ flags) {
+// Two stages so that a handful of rows still uses the whole device: each block
+// of stage one scans a chunk of a row (four independent loads in flight per
+// thread) and leaves its best (value, index) and flag; stage two reduces the
+// chunks of a row.
+constexpr int kArgmaxChunk = 4096;
+
+__global__ void __launch_bounds__(256)
+argmax_chunks_kernel(const float* __restrict__ logits, int vocab, int chunks, float* __restrict__ part_v,
+                     int* __restrict__ part_i, int* __restrict__ part_bad) {
     __shared__ ArgMax scratch[32];
     __shared__ int bad;
     if (threadIdx.x == 0) bad = 0;
     __syncthreads();
-    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int r = blockIdx.y, c = blockIdx.x;
+    const float* row = logits + (size_t)r * vocab;
+    const int lo = c * kArgmaxChunk, hi = min(vocab, lo + kArgmaxChunk);
     ArgMax a{-INFINITY, 0x7fffffff};
     bool nonfinite = false;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (!isfinite(v)) nonfinite = true;
-        a = better(a, ArgMax{v, i});
+    for (int i = lo + threadIdx.x; i < hi; i += 4 * blockDim.x) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const int e = i + j * blockDim.x; v[j] = e < hi ? row[e] : -INFINITY; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = i + j * blockDim.x;
+            if (e < hi) { if (!isfinite(v[j])) nonfinite = true; a = better(a, ArgMax{v[j], e}); }
+        }
     }
     if (nonfinite) bad = 1;
     a = block_argmax(a, scratch);
     if (threadIdx.x == 0) {
-        tokens[blockIdx.x] = a.i == 0x7fffffff ? 0 : a.i;
-        if (flags) flags[blockIdx.x] = bad;
+        part_v[(size_t)r * chunks + c] = a.v;
+        part_i[(size_t)r * chunks + c] = a.i;
+        part_bad[(size_t)r * chunks + c] = bad;
+    }
+}
+
+__global__ void __launch_bounds__(128)
+argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                    const int* __restrict__ part_bad, int chunks, int* __restrict__ tokens, int* __restrict__ flags) {
+    __shared__ ArgMax scratch[32];
+    __shared__ int bad;
+    if (threadIdx.x == 0) bad = 0;
+    __syncthreads();
+    const int r = blockIdx.x;
+    ArgMax a{-INFINITY, 0x7fffffff};
+    bool any_bad = false;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        a = better(a, ArgMax{part_v[(size_t)r * chunks + c], part_i[(size_t)r * chunks + c]});
+        if (part_bad[(size_t)r * chunks + c]) any_bad = true;
+    }
+    if (any_bad) bad = 1;
+    a = block_argmax(a, scratch);
+    if (threadIdx.x == 0) {
+        tokens[r] = a.i == 0x7fffffff ? 0 : a.i;
+        if (flags) flags[r] = bad;
     }
 }
 
@@ -273,12 +310,25 @@ sample_kernel(const float* __restrict__ logits, int vocab, const int* __restrict
 
 using namespace mdma;
 
+// Floats (4-byte words) of scratch mdma_argmax needs for these sizes.
+extern "C" long mdma_argmax_scratch(int n_rows, int vocab) {
+    return 3l * n_rows * ((vocab + kArgmaxChunk - 1) / kArgmaxChunk);
+}
+
 extern "C" int mdma_argmax(const float* logits, int n_rows, int vocab, int* tokens, int* flags,
-                           cudaStream_t stream) {
+                           float* scratch, long scratch_words, cudaStream_t stream) {
     MDMA_REQUIRE(vocab > 0 && n_rows >= 0, "argmax: bad sizes");
     if (n_rows == 0) return 0;
-    argmax_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, vocab, tokens, flags);
-    MDMA_LAUNCH_OK("argmax");
+    const int chunks = (vocab + kArgmaxChunk - 1) / kArgmaxChunk;
+    MDMA_REQUIRE(n_rows <= 65535, "argmax: too many rows");
+    MDMA_REQUIRE(scratch && scratch_words >= 3l * n_rows * chunks, "argmax: %ld words of scratch needed, %ld given", 3l * n_rows * chunks, scratch_words);
+    float* part_v = scratch;
+    int* part_i = reinterpret_cast<int*>(scratch + (size_t)n_rows * chunks);
+    int* part_bad = part_i + (size_t)n_rows * chunks;
+    argmax_chunks_kernel<<<dim3(chunks, n_rows), 256, 0, stream>>>(logits, vocab, chunks, part_v, part_i, part_bad);
+    MDMA_LAUNCH_OK("argmax_chunks");
+    argmax_final_kernel<<<n_rows, 128, 0, stream>>>(part_v, part_i, part_bad, chunks, tokens, flags);
+    MDMA_LAUNCH_OK("argmax_final");
     return 0;
 }
 

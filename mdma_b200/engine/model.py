@@ -99,6 +99,9 @@ class DecoderModel:
             site = n if entry.cache is None else entry.cache
             self.blocks[entry.layer].forward(ctx, x, cache.view(site, state_site=n),
                                              owns_cache=entry.cache is None)
+        if ctx.rt.gemm == "tensor":
+            from .. import ops_tensor
+            ops_tensor.flush_pending(x.device)
         if ctx.n_want:
             h = ctx.buf("h_rows", self.spec.hidden_size)
             self.final_norm.forward(ctx, x, h, rows=ctx.want_rows, n_rows=ctx.n_want)

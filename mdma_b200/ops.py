@@ -70,8 +70,10 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> Non
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
-    """out[i] = rmsnorm(x[rows[i]] or x[i]) * w; x is the float residual stream."""
+            rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+            partial: Optional[torch.Tensor] = None, splits: int = 0, split_stride: int = 0) -> None:
+    """out[i] = rmsnorm(x[rows[i]] or x[i]) * w; x is the float residual stream.  With
+    `partial` [splits, rows, width] the rows of x are first completed: x += sum of the partials."""
     _need_cuda(x, w, out, rows)
     assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
     width = x.shape[-1]
@@ -81,7 +83,8 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
     if rows is not None:
         assert rows.dtype == torch.int32
     _call("core", "mdma_rmsnorm", _ptr(x), _ptr(w), _i(dtype_code(w.dtype)), _ptr(rows), _ptr(out),
-          _i(dtype_code(out.dtype)), _i(n), _i(width), _f(eps), _stream())
+          _i(dtype_code(out.dtype)), _i(n), _i(width), _f(eps), _ptr(partial), _i(splits if partial is not None else 0),
+          ctypes.c_long(split_stride), _stream())
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = GEMM_STORE,
@@ -104,7 +107,10 @@ def rope_cache_write(qkv: torch.Tensor, n_tokens: int, tok_seq, tok_pos, seq_slo
                      k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                      page_table: Optional[torch.Tensor], max_pages: int, page_size: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
-                     interleaved: bool, write_kv: bool) -> None:
+                     interleaved: bool, write_kv: bool, partial: Optional[torch.Tensor] = None,
+                     splits: int = 0, split_stride: int = 0) -> None:
+    """Rotate q (in place) and k, write k and v to the cache.  With `partial`
+    [splits, tokens, row width] floats the projection row is their sum instead of qkv's content."""
     _need_cuda(qkv, tok_seq, tok_pos, seq_slot, inv_freq, k_cache, v_cache, page_table)
     assert qkv.stride(1) == 1 and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2
     if write_kv:
@@ -112,7 +118,8 @@ def rope_cache_write(qkv: torch.Tensor, n_tokens: int, tok_seq, tok_pos, seq_slo
         assert k_cache.is_contiguous() and v_cache.is_contiguous()
         assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
     _call("core", "mdma_rope_cache_write", _ptr(qkv), _i(dtype_code(qkv.dtype)), _i(qkv.stride(0)),
-          _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(inv_freq), _ptr(k_cache), _ptr(v_cache),
+          _ptr(partial), _i(splits if partial is not None else 0), ctypes.c_long(split_stride),
+          _i(qkv.shape[1]), _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_slot), _ptr(inv_freq), _ptr(k_cache), _ptr(v_cache),
           _ptr(page_table), _i(max_pages), _i(page_size),
           _i(n_tokens), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(rotary_dim), _i(int(interleaved)),
           _i(int(write_kv)), _stream())
@@ -140,13 +147,25 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
           _i(rows.numel()), _i(x.shape[1]), _stream())
 
 
+_argmax_scratch: dict = {}
+
+
 def argmax(logits: torch.Tensor, tokens: torch.Tensor, flags: Optional[torch.Tensor] = None,
            n_rows: Optional[int] = None) -> None:
+    """tokens[r] = index of the largest logit of row r (the lowest index among equals);
+    flags[r] = 1 if the row holds a value that is not finite."""
     _need_cuda(logits, tokens, flags)
     assert logits.dtype == torch.float32 and logits.is_contiguous() and tokens.dtype == torch.int32
     n = logits.shape[0] if n_rows is None else n_rows
+    need = 3 * max(n, 1) * (-(-logits.shape[1] // 4096))
+    scratch = _argmax_scratch.get(logits.device.index)
+    if scratch is None or scratch.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("argmax scratch cannot grow during graph capture")
+        scratch = _argmax_scratch[logits.device.index] = torch.empty(max(need, 1 << 16), dtype=torch.float32,
+                                                                     device=logits.device)
     _call("core", "mdma_argmax", _ptr(logits), _i(n), _i(logits.shape[1]), _ptr(tokens), _ptr(flags),
-          _stream())
+          _ptr(scratch), ctypes.c_long(scratch.numel()), _stream(), launches=2)
 
 
 def sample(logits: torch.Tensor, uniforms: torch.Tensor, tokens: torch.Tensor, probs_scratch: torch.Tensor,

@@ -18,7 +18,8 @@ _state: dict = {}
 def _device_state(device: torch.device) -> dict:
     st = _state.get(device.index)
     if st is None:
-        st = {"status": torch.zeros(4, dtype=torch.int32, device=device),
+        st = {"pending": None,
+              "status": torch.zeros(4, dtype=torch.int32, device=device),
               "scratch": torch.empty(1 << 20, dtype=torch.float32, device=device),
               "sms": torch.cuda.get_device_properties(device).multi_processor_count}
         _state[device.index] = st
@@ -52,10 +53,48 @@ def reserve_scratch(device: torch.device, floats: int) -> None:
         st["scratch"] = torch.empty(floats, dtype=torch.float32, device=device)
 
 
+class Pending:
+    """Partial sums of a K-split product that still wait in the scratch to be added
+    up into (or onto) `target`: [splits, rows, cols] floats."""
+    __slots__ = ("target_ptr", "target", "mode", "splits", "rows", "cols")
+
+    def __init__(self, target, mode, splits, rows, cols):
+        self.target, self.target_ptr = target, target.data_ptr()
+        self.mode, self.splits, self.rows, self.cols = mode, splits, rows, cols
+
+
+def flush_pending(device: torch.device) -> None:
+    """Finish a deferred K-split reduction with the plain reduce kernel."""
+    st = _state.get(device.index)
+    if st is None or st.get("pending") is None:
+        return
+    pend: Pending = st.pop("pending")
+    st["pending"] = None
+    out = pend.target
+    _call("tensor", "mdma_splitk_reduce", _i(pend.mode), _ptr(st["scratch"]), _i(pend.splits), _i(pend.rows),
+          _i(pend.cols), _ptr(out), _i(out.stride(0)), _i(int(out.dtype == torch.float32)), _stream())
+
+
+def take_pending(target: torch.Tensor, mode: int, rows: int):
+    """If partial sums for exactly this target wait in the scratch, hand them to the caller, who
+    will add them up itself: returns (scratch, splits, floats per split) or None."""
+    st = _state.get(target.device.index)
+    if st is None or st.get("pending") is None:
+        return None
+    pend: Pending = st["pending"]
+    if (pend.target_ptr != target.data_ptr() or pend.mode != mode or pend.rows != rows
+            or pend.cols != target.shape[1] or target.stride(0) != pend.cols):
+        return None
+    st["pending"] = None
+    return st["scratch"], pend.splits, pend.rows * pend.cols
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GEMM_STORE,
          w2: Optional[torch.Tensor] = None, m: Optional[int] = None,
-         bn: Optional[int] = None, splits: Optional[int] = None) -> None:
-    """out[:m] (=, +=) a[:m] @ w.T on the tensor cores; SwiGLU mode takes gate=w, up=w2."""
+         bn: Optional[int] = None, splits: Optional[int] = None, defer: bool = False) -> None:
+    """out[:m] (=, +=) a[:m] @ w.T on the tensor cores; SwiGLU mode takes gate=w, up=w2.
+    `defer`: if the product is split over K, leave its partial sums for the next kernel
+    (a norm or the rotary write) to add up; see `take_pending`."""
     _need_cuda(a, w, out, w2)
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("the tensor-core product takes bfloat16 operands")
@@ -66,6 +105,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
     if out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError(f"output dtype {out.dtype} is not supported")
     st = _device_state(a.device)
+    flush_pending(a.device)
     if bn is None or splits is None:
         pbn, psplits = gemm_plan(mode, M, N, K, st["sms"])
         bn = bn or pbn
@@ -75,10 +115,14 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("split-K scratch is too small and cannot grow during graph capture")
         reserve_scratch(a.device, need)
+    used = ctypes.c_int(1)
     _call("tensor", "mdma_gemm_tc", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), _ptr(out),
           _i(int(out.dtype == torch.float32)), _i(out.stride(0)), _i(M), _i(N), _i(K), _i(bn), _i(splits),
-          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]), _stream(),
-          launches=2 if splits > 1 else 1)
+          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]),
+          _i(int(defer)), ctypes.byref(used), _stream(),
+          launches=1 if (splits == 1 or defer) else 2)
+    if defer and used.value > 1:
+        st["pending"] = Pending(out, mode, used.value, M, N)
 
 
 def attention_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
@@ -104,6 +148,7 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
         raise KernelError("the tensor-core attention takes bfloat16")
     assert qkv.stride(1) == 1 and out.is_contiguous() and out.shape[1] == n_heads * head_dim
     st = _device_state(qkv.device)
+    flush_pending(qkv.device)
     if splits is None:
         splits = attention_splits(ctx.n_seqs, ctx.max_new, ctx.max_len, n_heads, n_kv_heads, st["sms"])
     need = ctx.n_tokens * n_heads * splits * (head_dim + 2) if splits > 1 else 0

@@ -82,7 +82,7 @@ class Attention(Part):
         n = ctx.n_tokens
         qkv = ctx.buf("qkv", self.row_width)
         out = ctx.buf("attn_out", self.q_width)
-        self.qkv_proj.store(h, qkv, n)
+        self.qkv_proj.store(h, qkv, n, defer=getattr(self.position, "fuses_pending", False))
         write = owns_cache and not self.shared_cache
         self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, view, write)
         if self.rt.attention == "fast" and self._fast_ok:
@@ -90,6 +90,9 @@ class Attention(Part):
             ops_tensor.attention(ctx, qkv, view, out, self.n_heads, self.n_kv_heads, self.head_dim,
                                  self.window, self.scale)
         else:
+            if self.rt.gemm == "tensor":
+                from .. import ops_tensor
+                ops_tensor.flush_pending(qkv.device)
             ops.attention_simple(qkv, n, view.k, view.v, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
                                  view.page_table, view.max_pages, view.page_size, out,
                                  self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)

@@ -21,7 +21,17 @@ class PreNormBlock:
 
     def forward(self, ctx, x, view, owns_cache=True):
         h = ctx.buf("normed", x.shape[1])
+        self._settle(ctx, x, self.mixer_norm)
         self.mixer_norm.forward(ctx, x, h)
         self.mixer.forward(ctx, h, x, view, owns_cache)
+        self._settle(ctx, x, self.ffn_norm)
         self.ffn_norm.forward(ctx, x, h)
         self.ffn.forward(ctx, h, x)
+
+    @staticmethod
+    def _settle(ctx, x, norm):
+        """A matrix product may have left partial sums of x for the next norm to add up;
+        a norm that does not do that gets x completed first."""
+        if ctx.rt.gemm == "tensor" and not getattr(norm, "fuses_pending", False):
+            from .. import ops_tensor
+            ops_tensor.flush_pending(x.device)

@@ -21,18 +21,24 @@ class Linear:
             from .. import ops_tensor
             self._tensor_ok = ops_tensor.gemm_supported(self.out_features, self.in_features)
 
-    def _run(self, mode: int, a: torch.Tensor, out: torch.Tensor, m: int) -> None:
+    def _run(self, mode: int, a: torch.Tensor, out: torch.Tensor, m: int, defer: bool = False) -> None:
         if self._tensor_ok:
             from .. import ops_tensor
-            ops_tensor.gemm(a, self.w, out, mode, self.w2, m)
+            ops_tensor.gemm(a, self.w, out, mode, self.w2, m, defer=defer)
         else:
+            if self.rt.gemm == "tensor":
+                from .. import ops_tensor
+                ops_tensor.flush_pending(a.device)
             ops.gemm_simt(a, self.w, out, mode, self.w2, m)
 
-    def store(self, a, out, m):
-        self._run(ops.GEMM_STORE, a, out, m)
+    def store(self, a, out, m, defer: bool = False):
+        """out = a W^T.  `defer`: a K-split product may leave its partial sums for the
+        next kernel to add up (the caller promises that kernel asks for them)."""
+        self._run(ops.GEMM_STORE, a, out, m, defer)
 
-    def accumulate(self, a, x, m):
-        self._run(ops.GEMM_ACCUMULATE, a, x, m)
+    def accumulate(self, a, x, m, defer: bool = True):
+        """x += a W^T.  Deferred by default: the norm that reads x next adds the partial sums."""
+        self._run(ops.GEMM_ACCUMULATE, a, x, m, defer)
 
     def swiglu(self, a, out, m):
         self._run(ops.GEMM_SWIGLU, a, out, m)

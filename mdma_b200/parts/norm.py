@@ -23,9 +23,19 @@ class RMSNorm(Part):
         super().bind(tensors, rt)
         self.weight = tensors["weight"]
 
+    fuses_pending = True        # adds up a deferred K-split product on x itself
+
     def forward(self, ctx, x, out, rows=None, n_rows=None):
-        ops.rmsnorm(x, self.weight, self.eps, out, rows,
-                    n_rows if n_rows is not None else (None if rows is not None else ctx.n_tokens))
+        n = n_rows if n_rows is not None else (None if rows is not None else ctx.n_tokens)
+        if self.rt.gemm == "tensor":
+            from .. import ops_tensor
+            pend = ops_tensor.take_pending(x, ops.GEMM_ACCUMULATE, ctx.n_tokens) if rows is None else None
+            if pend is not None:
+                scratch, splits, stride = pend
+                ops.rmsnorm(x, self.weight, self.eps, out, None, n, scratch, splits, stride)
+                return
+            ops_tensor.flush_pending(x.device)
+        ops.rmsnorm(x, self.weight, self.eps, out, rows, n)
 
     def resident_bytes(self):
         return self.weight.numel() * self.weight.element_size()

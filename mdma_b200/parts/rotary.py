@@ -60,8 +60,19 @@ class Rotary(Part):
         super().bind(tensors, rt)
         self.inv_freq = self.table_host.to(rt.device)
 
+    fuses_pending = True        # adds up a deferred K-split projection itself
+
     def encode_and_store(self, ctx, qkv, n_heads, n_kv_heads, head_dim, view, write_kv):
+        partial, splits, stride = None, 0, 0
+        if self.rt.gemm == "tensor":
+            from .. import ops_tensor
+            pend = ops_tensor.take_pending(qkv, ops.GEMM_STORE, ctx.n_tokens)
+            if pend is not None:
+                partial, splits, stride = pend
+            else:
+                ops_tensor.flush_pending(qkv.device)
         ops.rope_cache_write(qkv, ctx.n_tokens, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot, self.inv_freq,
                              view.k if write_kv else None, view.v if write_kv else None,
                              view.page_table if write_kv else None, view.max_pages, view.page_size,
-                             n_heads, n_kv_heads, head_dim, self.rotary_dim, self.interleaved, write_kv)
+                             n_heads, n_kv_heads, head_dim, self.rotary_dim, self.interleaved, write_kv,
+                             partial, splits, stride)

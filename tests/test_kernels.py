@@ -37,7 +37,7 @@ def test_embed_rows(dtype):
     assert bool((out[5:] == 9.0).all())
 
 
-@pytest.mark.parametrize("width", [4099, 96, 8])
+@pytest.mark.parametrize("width", [4099, 96, 8, 4096, 12000, 20000])
 @pytest.mark.parametrize("odt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                      (torch.bfloat16, torch.float32)])
 def test_rmsnorm(width, odt, wdt):
@@ -54,6 +54,50 @@ def test_rmsnorm(width, odt, wdt):
     ops.rmsnorm(x, w, 3e-6, out, rows=rows)
     want = plain_rmsnorm(x[[5, 0, 5]].double().cpu(), w.double().cpu(), 3e-6)
     close(out[:3], want, 1e-5 if odt == torch.float32 else 0, 0 if odt == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("width,splits", [(4096, 5), (120, 2), (9000, 3), (17000, 2)])
+def test_rmsnorm_adds_split_partials_first(width, splits):
+    """x += sum of the partial sums, then the norm of the completed row; x itself is updated."""
+    ops = ops_mod()
+    torch.manual_seed(width)
+    T = 5
+    x = torch.randn(T + 1, width, device=DEV)
+    x0 = x.clone()
+    partial = torch.randn(splits, T, width, device=DEV)
+    w = (torch.rand(width, device=DEV) + 0.5).bfloat16()
+    out = torch.full((T + 1, width), 9.0, device=DEV, dtype=torch.bfloat16)
+    ops.rmsnorm(x, w, 1e-5, out, None, T, partial, splits, T * width)
+    full = x0[:T].double().cpu()
+    for s_ in range(splits):
+        full = (full.float() + partial[s_].cpu()).double()        # float adds in split order, as the kernel does
+    close(x[:T], full, 0.0)
+    assert torch.equal(x[T:], x0[T:]) and bool((out[T:] == 9.0).all())
+    close(out[:T], plain_rmsnorm(full, w.double().cpu(), 1e-5), 0, 1e-2)
+
+
+def test_rope_reads_split_partials():
+    ops = ops_mod()
+    torch.manual_seed(3)
+    H, K, hd, page, max_pages, T, splits = 4, 2, 32, 16, 8, 6, 3
+    width = (H + 2 * K) * hd
+    partial = torch.randn(splits, T, width, device=DEV)
+    summed = partial.sum(0)
+    inv = plain_inv_freq(hd, 1e4, None).to(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    table = torch.arange(8, dtype=torch.int32, device=DEV).reshape(1, 8)
+    res = []
+    for use_partial in (True, False):
+        qkv = torch.zeros(T, width, device=DEV, dtype=torch.bfloat16) if use_partial else summed.bfloat16()
+        kc, vc = paged_cache(8, page, K, hd, torch.bfloat16)
+        ops.rope_cache_write(qkv, T, i32([0] * T), i32(list(range(20, 20 + T))), i32([0]), inv, kc, vc, table,
+                             max_pages, page, H, K, hd, hd, False, True,
+                             partial if use_partial else None, splits, T * width)
+        res.append((qkv[:, :H * hd].clone(), kc.clone(), vc.clone()))
+    for a, b in zip(*res):
+        close(a, b.double(), 2e-2, 1e-2)          # the partial path rounds once, the other twice
+    want_q = plain_rope(summed[:, :H * hd].double().cpu().reshape(T, H, hd), torch.arange(20, 20 + T), inv.cpu(), "split_half")
+    close(res[0][0].reshape(T, H, hd), want_q, 1e-2, 1e-2)
 
 
 def paged_cache(n_pages, page, kvh, d, dtype):
