@@ -75,6 +75,8 @@ attention_mma_kernel(const AttnParams p) {
     const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t sK = sQ + kTile, sV = sK + 2 * kTile;
 
+    chain_release();
+    chain_wait();
     const int seq = blockIdx.y;
     const int kvh = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
     const int row0_seq = p.seq_start[seq];
@@ -248,9 +250,221 @@ attention_mma_kernel(const AttnParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// Decode: every sequence brings one token.  The G query heads of a kv head are
+// the (up to 16) rows of one MMA tile, so nothing is computed for padding rows
+// beyond that tile.  A block of four warps works on one (sequence, kv head,
+// split); its warps take the key blocks of the split in turn (warp w: blocks
+// w, w+4, ...), each with its own running maximum, sum and output, loading its
+// keys and values into a private shared-memory buffer (K of the next block is
+// fetched while P*V of this one runs).  At the end the four states are combined
+// through shared memory in warp order and written as the final output or as
+// this split's partial.  Tiles of 32 keys keep a block's shared memory small
+// enough for three blocks per SM, which is what hides the load latency.
+constexpr int kDecodeKeys = 32;
+template <int DMAX, int KB>      // KB: keys per warp tile
+__global__ void __launch_bounds__(kAttnThreads, 3)
+attention_decode_kernel(const AttnParams p) {
+    constexpr int kChunks = DMAX / 8;
+    constexpr int kTile = KB * DMAX * 2;             // one 64-key K or V tile
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t s0 = (uint32_t)__cvta_generic_to_shared(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sQ = s0;                              // 16 rows x DMAX
+    const uint32_t sK = s0 + 16 * DMAX * 2 + warp * 2 * kTile, sV = sK + kTile;
+
+    chain_release();
+    chain_wait();
+    const int seq = blockIdx.y;
+    const int kvh = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+    const int token = p.seq_start[seq];
+    const int pos = p.seq_pos0[seq];
+    const int* pages = p.page_table + (size_t)p.seq_slot[seq] * p.max_pages;
+    const int D = p.head_dim, G = p.group, d_chunks = D / 8;
+    const int first_key = p.window > 0 ? max(0, pos + 1 - p.window) : 0;
+    const int blk_lo = first_key / KB, blk_hi = pos / KB + 1;
+    const int per = (blk_hi - blk_lo + p.splits - 1) / p.splits;
+    const int b0 = blk_lo + split * per, b1 = min(blk_hi, b0 + per);
+    const bool page_aligned = (p.page_size % KB) == 0;
+
+    // Q rows (heads of the group) -> shared, zero beyond G and beyond D
+    for (int i = threadIdx.x; i < 16 * kChunks; i += kAttnThreads) {
+        const int r = i / kChunks, c = i % kChunks;
+        const bool valid = r < G && c < d_chunks;
+        const __nv_bfloat16* src = p.q + (size_t)token * p.q_stride + (size_t)(kvh * G + (valid ? r : 0)) * D + (valid ? c : 0) * 8;
+        cp_async_16(sQ + tile_offset<DMAX>(r, c), src, valid);
+    }
+    auto load_tile = [&](const __nv_bfloat16* cache, uint32_t dst, int blk) {
+        size_t base = 0;
+        if (page_aligned) {
+            const int key0 = blk * KB;
+            base = ((size_t)pages[key0 / p.page_size] * p.page_size + key0 % p.page_size) * p.n_kv_heads;
+        }
+#pragma unroll 4
+        for (int i = lane; i < KB * kChunks; i += 32) {
+            const int r = i / kChunks, c = i % kChunks;
+            const int key = blk * KB + r;
+            const bool valid = key <= pos && c < d_chunks;
+            size_t off = 0;
+            if (valid) {
+                if (page_aligned) off = ((base + (size_t)r * p.n_kv_heads) + kvh) * D + c * 8;
+                else off = (((size_t)pages[key / p.page_size] * p.page_size + key % p.page_size) * p.n_kv_heads + kvh) * D + c * 8;
+            }
+            cp_async_16(dst + tile_offset<DMAX>(r, c), cache + off, valid);
+        }
+    };
+    int blk = b0 + warp;
+    if (blk < b1) load_tile(p.k_cache, sK, blk);
+    cp_async_commit();                                   // group: Q (+ first K)
+    if (blk < b1) load_tile(p.v_cache, sV, blk);
+    cp_async_commit();                                   // group: first V
+    cp_async_wait<1>();
+    __syncthreads();                                     // Q visible to all warps
+
+    uint32_t qf[DMAX / 16][4];
+#pragma unroll
+    for (int kd = 0; kd < DMAX / 16; ++kd)
+        ldmatrix_x4(sQ + tile_offset<DMAX>(lane & 15, kd * 2 + (lane >> 4)), qf[kd][0], qf[kd][1], qf[kd][2], qf[kd][3]);
+
+    const int win = p.window > 0 ? pos + 1 - p.window : 0;
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int n = 0; n < DMAX / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+    for (; blk < b1; blk += 4) {
+        cp_async_wait<1>();                              // this block's K has landed (its V may be in flight)
+        __syncwarp();
+        float s[KB / 8][4];
+#pragma unroll
+        for (int n = 0; n < KB / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+        for (int kd = 0; kd < DMAX / 16; ++kd) {
+            if (kd * 16 < D) {
+#pragma unroll
+                for (int n2 = 0; n2 < KB / 16; ++n2) {
+                    uint32_t k0, k1, k2, k3;
+                    const int krow = n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    ldmatrix_x4(sK + tile_offset<DMAX>(krow, kd * 2 + ((lane >> 3) & 1)), k0, k1, k2, k3);
+                    mma_16816(s[n2 * 2], qf[kd][0], qf[kd][1], qf[kd][2], qf[kd][3], k0, k1);
+                    mma_16816(s[n2 * 2 + 1], qf[kd][0], qf[kd][1], qf[kd][2], qf[kd][3], k2, k3);
+                }
+            }
+        }
+        __syncwarp();
+        const bool more = blk + 4 < b1;
+        if (more) load_tile(p.k_cache, sK, blk + 4);     // K buffer is free: fetch the next block's keys
+        cp_async_commit();
+        const int key_base = blk * KB + (lane & 3) * 2;
+        float mx_lo = m_lo, mx_hi = m_hi;
+#pragma unroll
+        for (int n = 0; n < KB / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key_base + n * 8 + e;
+                const bool vis = key <= pos && key >= win;
+                const float v_lo = vis ? s[n][e] * p.scale_log2 : -INFINITY;
+                const float v_hi = vis ? s[n][2 + e] * p.scale_log2 : -INFINITY;
+                s[n][e] = v_lo; s[n][2 + e] = v_hi;
+                mx_lo = fmaxf(mx_lo, v_lo); mx_hi = fmaxf(mx_hi, v_hi);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float ref_lo = mx_lo == -INFINITY ? 0.f : mx_lo, ref_hi = mx_hi == -INFINITY ? 0.f : mx_hi;
+        const float corr_lo = exp2f(m_lo - ref_lo), corr_hi = exp2f(m_hi - ref_hi);
+        m_lo = mx_lo; m_hi = mx_hi;
+        float sum_lo = 0.f, sum_hi = 0.f;
+        uint32_t pa[KB / 16][4];
+#pragma unroll
+        for (int n = 0; n < KB / 8; ++n) {
+            const float p0 = exp2f(s[n][0] - ref_lo), p1 = exp2f(s[n][1] - ref_lo);
+            const float p2 = exp2f(s[n][2] - ref_hi), p3 = exp2f(s[n][3] - ref_hi);
+            sum_lo += p0 + p1; sum_hi += p2 + p3;
+            pa[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+            pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l_lo = l_lo * corr_lo + sum_lo; l_hi = l_hi * corr_hi + sum_hi;
+#pragma unroll
+        for (int n = 0; n < DMAX / 8; ++n) {
+            o[n][0] *= corr_lo; o[n][1] *= corr_lo; o[n][2] *= corr_hi; o[n][3] *= corr_hi;
+        }
+        cp_async_wait<1>();                              // this block's V has landed (next K may be in flight)
+        __syncwarp();
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; ++kk) {
+#pragma unroll
+            for (int n2 = 0; n2 < DMAX / 16; ++n2) {
+                if (n2 * 16 < D) {
+                    uint32_t v0, v1, v2, v3;
+                    const int vrow = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                    ldmatrix_x4_trans(sV + tile_offset<DMAX>(vrow, n2 * 2 + (lane >> 4)), v0, v1, v2, v3);
+                    mma_16816(o[n2 * 2], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], v0, v1);
+                    mma_16816(o[n2 * 2 + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], v2, v3);
+                }
+            }
+        }
+        __syncwarp();
+        if (more) load_tile(p.v_cache, sV, blk + 4);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+    // ---- combine the four warps' states in warp order ---------------------------
+    // layout in shared memory (reusing the tiles): per warp [16 rows][DMAX + 2] floats
+    __syncthreads();
+    float* comb = reinterpret_cast<float*>(smem);
+    constexpr int kRowF = DMAX + 2;
+    {
+        float* mine = comb + (size_t)warp * 16 * kRowF;
+        const int r_lo = lane >> 2, r_hi = r_lo + 8;
+#pragma unroll
+        for (int n = 0; n < DMAX / 8; ++n) {
+            const int d = n * 8 + (lane & 3) * 2;
+            mine[r_lo * kRowF + d] = o[n][0]; mine[r_lo * kRowF + d + 1] = o[n][1];
+            mine[r_hi * kRowF + d] = o[n][2]; mine[r_hi * kRowF + d + 1] = o[n][3];
+        }
+        if ((lane & 3) == 0) {
+            mine[r_lo * kRowF + DMAX] = m_lo; mine[r_lo * kRowF + DMAX + 1] = l_lo;
+            mine[r_hi * kRowF + DMAX] = m_hi; mine[r_hi * kRowF + DMAX + 1] = l_hi;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * D; i += kAttnThreads) {
+        const int r = i / D, d = i % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, comb[((size_t)w * 16 + r) * kRowF + DMAX]);
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = comb[((size_t)w * 16 + r) * kRowF + DMAX];
+            if (mw != -INFINITY) {
+                const float f = exp2f(mw - m);
+                l += f * comb[((size_t)w * 16 + r) * kRowF + DMAX + 1];
+                acc += f * comb[((size_t)w * 16 + r) * kRowF + d];
+            }
+        }
+        const int head = kvh * G + r;
+        if (p.splits == 1) {
+            p.out[((size_t)token * p.n_heads + head) * D + d] = __float2bfloat16_rn(acc / l);
+        } else {
+            const size_t slot = ((size_t)token * p.n_heads + head) * p.splits + split;
+            p.part_o[slot * D + d] = acc;
+            if (d == 0) { p.part_ml[slot * 2] = m; p.part_ml[slot * 2 + 1] = l; }
+        }
+    }
+}
+
 // out[token, head, :] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, splits taken in order.
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int splits, int head_dim) {
+    chain_release();
+    chain_wait();
     const size_t th = blockIdx.x;                   // token * heads + head
     const float* ml = part_ml + th * splits * 2;
     float m = -INFINITY;
@@ -308,20 +522,33 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
         p.part_ml = scratch + (long)n_tokens * n_heads * splits * head_dim;
     }
     dim3 grid((max_new + p.tile_tokens - 1) / p.tile_tokens, n_seqs, n_kv_heads * splits);
-    if (head_dim <= 64) {
+    if (max_new == 1 && p.group <= 16) {
+        // one token per sequence: the decode kernel (no padding rows beyond one 16-row tile)
+        if (head_dim <= 64) {
+            constexpr int bytes = 16 * 64 * 2 + 4 * 2 * kDecodeKeys * 64 * 2;
+            static bool once = false;
+            if (!once) { cudaFuncSetAttribute(attention_decode_kernel<64, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
+            launch_chained(attention_decode_kernel<64, kDecodeKeys>, grid, dim3(kAttnThreads), bytes, stream, p);
+        } else {
+            constexpr int bytes = 16 * 128 * 2 + 4 * 2 * kDecodeKeys * 128 * 2;
+            static bool once = false;
+            if (!once) { cudaFuncSetAttribute(attention_decode_kernel<128, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
+            launch_chained(attention_decode_kernel<128, kDecodeKeys>, grid, dim3(kAttnThreads), bytes, stream, p);
+        }
+    } else if (head_dim <= 64) {
         constexpr int bytes = 5 * kRows * 64 * 2;
         static bool once = false;
         if (!once) { cudaFuncSetAttribute(attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
-        attention_mma_kernel<64><<<grid, kAttnThreads, bytes, stream>>>(p);
+        launch_chained(attention_mma_kernel<64>, grid, dim3(kAttnThreads), bytes, stream, p);
     } else {
         constexpr int bytes = 5 * kRows * 128 * 2;
         static bool once = false;
         if (!once) { cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
-        attention_mma_kernel<128><<<grid, kAttnThreads, bytes, stream>>>(p);
+        launch_chained(attention_mma_kernel<128>, grid, dim3(kAttnThreads), bytes, stream, p);
     }
     MDMA_LAUNCH_OK("attention_mma");
     if (splits > 1) {
-        attention_merge_kernel<<<n_tokens * n_heads, 64, 0, stream>>>(p.part_o, p.part_ml, p.out, splits, head_dim);
+        launch_chained(attention_merge_kernel, dim3(n_tokens * n_heads), dim3(64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, splits, head_dim);
         MDMA_LAUNCH_OK("attention_merge");
     }
     return 0;

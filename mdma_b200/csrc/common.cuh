@@ -6,6 +6,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace mdma {
 
@@ -30,6 +31,34 @@ static inline int fail(const char* fmt, ...) {
 #define MDMA_LAUNCH_OK(name) \
     do { cudaError_t e_ = cudaGetLastError(); \
          if (e_ != cudaSuccess) return ::mdma::fail("%s: launch failed: %s", name, cudaGetErrorString(e_)); } while (0)
+
+// Programmatic dependent launch.  A kernel launched with `launch_chained` may start
+// while the kernel before it in the stream is still running; it must call
+// `chain_wait()` before it reads or writes anything that earlier kernels touch
+// (reading weights before that is fine), and calls `chain_release()` early so the
+// kernel after it can begin its own prologue.  Without the launch attribute both
+// are no-ops.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool chaining_enabled() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("MDMA_CHAIN"); on = (e && e[0] == '0') ? 0 : 1; }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = chaining_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }

@@ -11,6 +11,8 @@ namespace mdma {
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int width, int vocab) {
+    chain_release();
+    chain_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * width;
@@ -35,6 +37,8 @@ template <typename TO, typename TW, int PER>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ partial, int splits,
                                size_t split_stride, const TW* __restrict__ w, const int* __restrict__ rows,
                                TO* __restrict__ y, int width, float eps) {
+    chain_release();
+    chain_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * width;
@@ -95,6 +99,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
                                         const int* __restrict__ page_table, int max_pages, int page_size,
                                         int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
                                         int interleaved, int write_kv) {
+    chain_release();
+    chain_wait();
     const int t = blockIdx.x;
     const int h = blockIdx.y;
     const int pos = tok_pos[t];
@@ -150,6 +156,8 @@ __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restric
 // position moves on by one.
 __global__ void advance_decode_kernel(const int* __restrict__ tokens, int* __restrict__ ids,
                                       int* __restrict__ tok_pos, int* __restrict__ seq_pos0, int n) {
+    chain_release();
+    chain_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     ids[i] = tokens[i];
@@ -162,13 +170,13 @@ static void launch_rmsnorm(float* x, const float* partial, int splits, size_t sp
                            const int* rows, TO* y, int n_rows, int width, float eps, cudaStream_t stream) {
     auto threads_for = [&](int per) { int t = ((width + per - 1) / per + 31) / 32 * 32; return t < 64 ? 64 : t; };
     if (width <= 4096)
-        rmsnorm_kernel<TO, TW, 4><<<n_rows, threads_for(4), 0, stream>>>(x, partial, splits, split_stride, w, rows, y, width, eps);
+        launch_chained(rmsnorm_kernel<TO, TW, 4>, dim3(n_rows), dim3(threads_for(4)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
     else if (width <= 8192)
-        rmsnorm_kernel<TO, TW, 8><<<n_rows, threads_for(8), 0, stream>>>(x, partial, splits, split_stride, w, rows, y, width, eps);
+        launch_chained(rmsnorm_kernel<TO, TW, 8>, dim3(n_rows), dim3(threads_for(8)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
     else if (width <= 16384)
-        rmsnorm_kernel<TO, TW, 16><<<n_rows, threads_for(16), 0, stream>>>(x, partial, splits, split_stride, w, rows, y, width, eps);
+        launch_chained(rmsnorm_kernel<TO, TW, 16>, dim3(n_rows), dim3(threads_for(16)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
     else
-        rmsnorm_kernel<TO, TW, 0><<<n_rows, 1024, 0, stream>>>(x, partial, splits, split_stride, w, rows, y, width, eps);
+        launch_chained(rmsnorm_kernel<TO, TW, 0>, dim3(n_rows), dim3(1024), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
 }
 
 }  // namespace mdma
@@ -179,7 +187,7 @@ extern "C" {
 
 int mdma_advance_decode(const int* tokens, int* ids, int* tok_pos, int* seq_pos0, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    advance_decode_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, ids, tok_pos, seq_pos0, n);
+    launch_chained(advance_decode_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, ids, tok_pos, seq_pos0, n);
     MDMA_LAUNCH_OK("advance_decode");
     return 0;
 }
@@ -191,7 +199,7 @@ int mdma_embed_rows(const void* table, int table_dtype, const int* ids, float* o
     MDMA_REQUIRE(n_tokens >= 0 && width > 0 && vocab > 0, "embed_rows: bad sizes");
     if (n_tokens == 0) return 0;
     MDMA_DISPATCH_DTYPE(table_dtype, T,
-        embed_rows_kernel<T><<<n_tokens, 256, 0, stream>>>((const T*)table, ids, out, width, vocab));
+        launch_chained(embed_rows_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table, ids, out, width, vocab));
     MDMA_LAUNCH_OK("embed_rows");
     return 0;
 }
@@ -227,7 +235,7 @@ int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const float* par
     int threads = 32;
     while (threads < head_dim / 2 && threads < 128) threads *= 2;
     MDMA_DISPATCH_DTYPE(dtype, T,
-        rope_cache_write_kernel<T><<<grid, threads, 0, stream>>>(
+        launch_chained(rope_cache_write_kernel<T>, grid, dim3(threads), 0, stream,
             (T*)qkv, row_stride, partial, splits, (size_t)split_stride, partial_width,
             tok_seq, tok_pos, seq_slot, inv_freq, (T*)k_cache, (T*)v_cache,
             page_table, max_pages, page_size, n_heads, n_kv_heads, head_dim, rotary_dim, interleaved, write_kv));

@@ -76,6 +76,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
     const int n_kb = kb_end - kb_begin;
 
+    chain_release();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
         ptx::mbar_init(acc_bar, 1);
@@ -96,8 +97,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         ptx::prefetch_tensormap(&map_w);
         ptx::prefetch_tensormap(&map_x);
         if (kDual) ptx::prefetch_tensormap(&map_w2);
-        int issued = 0;
-        for (int i = 0; i < n_kb; ++i) {
+        // Weights do not depend on earlier kernels: fill the ring with weight boxes first,
+        // then wait for the kernel before this one and fetch the matching activation boxes.
+        const int ahead = min(n_kb, kStages);
+        for (int i = 0; i < ahead; ++i) {
+            const uint32_t stage = base + i * S::kStage;
+            ptx::mbar_expect_tx(full_bar(i), S::kA * (kDual ? 2 : 1) + S::kB);
+            const int k = (kb_begin + i) * kBK;
+            ptx::tma_load_2d(stage, &map_w, full_bar(i), k, f0);
+            if (kDual) ptx::tma_load_2d(stage + S::kA, &map_w2, full_bar(i), k, f0);
+        }
+        chain_wait();
+        for (int i = 0; i < ahead; ++i)
+            ptx::tma_load_2d(base + i * S::kStage + S::kA * (kDual ? 2 : 1), &map_x, full_bar(i), (kb_begin + i) * kBK, t0);
+        int issued = ahead;
+        for (int i = ahead; i < n_kb; ++i) {
             const int s = i % kStages;
             if (!ptx::mbar_wait(empty_bar(s), ((i / kStages) & 1) ^ 1, abort_flag)) break;
             const uint32_t stage = base + s * S::kStage;
@@ -140,6 +154,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---- epilogue: TMEM -> registers -> global ----------------------------
         const int quad = warp & 3;              // the TMEM lanes this warp may read
         const int f = f0 + quad * 32 + lane;
+        chain_wait();                           // the output may still be read by an earlier kernel
         const bool ok = ptx::mbar_wait(acc_bar, 0, abort_flag);
         ptx::tc_fence_after_sync();
         if (ok && n_kb > 0) {
@@ -193,6 +208,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 template <int MODE>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int n_tokens, int n_features,
                                      void* __restrict__ out, int ldo, int out_f32) {
+    chain_release();
+    chain_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)n_tokens * n_features;
     if (i >= total) return;
@@ -282,7 +299,7 @@ static int run_tc(const void* x, int ldx, const void* w, const void* w2, int K, 
         if (int rc = make_map_2d(&mw2, w2, (uint64_t)p.n_features, (uint64_t)K, (uint64_t)K * 2, kBM)) return rc;
     if (int rc = make_map_2d(&mx, x, (uint64_t)p.n_tokens, (uint64_t)K, (uint64_t)ldx * 2, BN)) return rc;
     dim3 grid((p.n_features + kBM - 1) / kBM, (p.n_tokens + BN - 1) / BN, splits);
-    gemm_tc_kernel<BN, MODE><<<grid, kTcThreads, S::kBytes, stream>>>(mw, mw2, mx, p);
+    launch_chained(gemm_tc_kernel<BN, MODE>, grid, dim3(kTcThreads), S::kBytes, stream, mw, mw2, mx, p);
     MDMA_LAUNCH_OK("gemm_tc");
     return 0;
 }
@@ -335,9 +352,9 @@ int mdma_splitk_reduce(int mode, const float* partial, int splits, int n_tokens,
     if (total == 0) return 0;
     const int blocks = (int)((total + 255) / 256);
     if (mode == kTcAccumulate)
-        splitk_reduce_kernel<kTcAccumulate><<<blocks, 256, 0, stream>>>(partial, splits, n_tokens, n_features, out, ldo, out_f32);
+        launch_chained(splitk_reduce_kernel<kTcAccumulate>, dim3(blocks), dim3(256), 0, stream, partial, splits, n_tokens, n_features, out, ldo, out_f32);
     else
-        splitk_reduce_kernel<kTcStore><<<blocks, 256, 0, stream>>>(partial, splits, n_tokens, n_features, out, ldo, out_f32);
+        launch_chained(splitk_reduce_kernel<kTcStore>, dim3(blocks), dim3(256), 0, stream, partial, splits, n_tokens, n_features, out, ldo, out_f32);
     MDMA_LAUNCH_OK("splitk_reduce");
     return 0;
 }

@@ -46,6 +46,8 @@ constexpr int kArgmaxChunk = 4096;
 __global__ void __launch_bounds__(256)
 argmax_chunks_kernel(const float* __restrict__ logits, int vocab, int chunks, float* __restrict__ part_v,
                      int* __restrict__ part_i, int* __restrict__ part_bad) {
+    chain_release();
+    chain_wait();
     __shared__ ArgMax scratch[32];
     __shared__ int bad;
     if (threadIdx.x == 0) bad = 0;
@@ -77,6 +79,8 @@ argmax_chunks_kernel(const float* __restrict__ logits, int vocab, int chunks, fl
 __global__ void __launch_bounds__(128)
 argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                     const int* __restrict__ part_bad, int chunks, int* __restrict__ tokens, int* __restrict__ flags) {
+    chain_release();
+    chain_wait();
     __shared__ ArgMax scratch[32];
     __shared__ int bad;
     if (threadIdx.x == 0) bad = 0;
@@ -325,9 +329,9 @@ extern "C" int mdma_argmax(const float* logits, int n_rows, int vocab, int* toke
     float* part_v = scratch;
     int* part_i = reinterpret_cast<int*>(scratch + (size_t)n_rows * chunks);
     int* part_bad = part_i + (size_t)n_rows * chunks;
-    argmax_chunks_kernel<<<dim3(chunks, n_rows), 256, 0, stream>>>(logits, vocab, chunks, part_v, part_i, part_bad);
+    launch_chained(argmax_chunks_kernel, dim3(chunks, n_rows), dim3(256), 0, stream, logits, vocab, chunks, part_v, part_i, part_bad);
     MDMA_LAUNCH_OK("argmax_chunks");
-    argmax_final_kernel<<<n_rows, 128, 0, stream>>>(part_v, part_i, part_bad, chunks, tokens, flags);
+    launch_chained(argmax_final_kernel, dim3(n_rows), dim3(128), 0, stream, (const float*)part_v, (const int*)part_i, (const int*)part_bad, chunks, tokens, flags);
     MDMA_LAUNCH_OK("argmax_final");
     return 0;
 }

@@ -132,11 +132,19 @@ def attention_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
 
 def attention_splits(n_seqs: int, max_new: int, max_len: int, n_heads: int, n_kv_heads: int, sms: int) -> int:
     """How many ways to divide a tile's keys so that the grid fills the device."""
-    tile_tokens = max(1, 64 // (n_heads // n_kv_heads))
+    group = n_heads // n_kv_heads
+    key_blocks = max(1, -(-max_len // 64))
+    if max_new == 1 and group <= 16:
+        # decode kernel: a block's four warps already take four key blocks at a time
+        blocks = n_seqs * n_kv_heads
+        if blocks >= 2 * sms:
+            return 1
+        rounds = -(-max_len // (32 * 4))           # four warps x 32 keys per round
+        return max(1, min(-(-3 * sms // blocks), rounds, 32))
+    tile_tokens = max(1, 64 // group)
     blocks = -(-max_new // tile_tokens) * n_seqs * n_kv_heads
     if blocks >= 2 * sms:
         return 1
-    key_blocks = max(1, -(-max_len // 64))
     return max(1, min(-(-2 * sms // blocks), key_blocks, 32))
 
 
