@@ -121,6 +121,8 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the shape has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement (profiling runs)")
+    ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill (profiling runs)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -176,6 +178,29 @@ def main() -> int:
             eng.release(s)
         return ms / steps, per_graph * steps, ctx_now
 
+    def time_prefill(T=2048):
+        times = []
+        for i in range(warmup + 5):
+            s = eng.acquire()
+            p = prompts(1, T)[0]
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([StepEntry(s, p, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            eng.release(s)
+            if i >= warmup:
+                times.append(e0.elapsed_time(e1))
+        ms_p = sorted(times)[len(times) // 2]
+        fl = prefill_flops(cfg, args.layers, T)
+        return {"value": round(T * 1000.0 / ms_p, 1), "tokens": T, "ms": round(ms_p, 3),
+                "frac": round(fl / (ms_p * 1e-3) / (bf16_tflops * 1e12), 4)}
+
+    if args.prefill_only:
+        print(json.dumps({"prefill": time_prefill(), "config": {"layers": args.layers, "layers_full": FULL_LAYERS}}))
+        return 0
+
     clock = ClockSampler()
     clock.start()
     ms_step, launches, ctx_end = time_decode(args.batch, args.steps)
@@ -186,17 +211,18 @@ def main() -> int:
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
 
     # end to end: host token lists in, host token lists out, through Generator.generate
-    stamps = []
-    g = Generator(eng, sampler)
-    n_e2e = args.steps + warmup + 1
-    g.generate(prompts(args.batch, args.prompt_len), max_tokens=warmup + 2)        # warm the path
-    g.generate(prompts(args.batch, args.prompt_len), max_tokens=n_e2e,
-               on_token=lambda r, t: stamps.append(time.perf_counter()) if r == args.batch - 1 else None)
-    # stamps[i] is taken after every sequence's i-th token reached the host
-    e2e_tokens = args.batch * args.steps
-    e2e_value = e2e_tokens / (stamps[-1] - stamps[-1 - args.steps])
-    e2e = {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
-           "d2h_bytes_per_step": 8 * args.batch}
+    e2e = None
+    if not args.no_e2e:
+        stamps = []
+        g = Generator(eng, sampler)
+        n_e2e = args.steps + warmup + 1
+        g.generate(prompts(args.batch, args.prompt_len), max_tokens=warmup + 2)        # warm the path
+        g.generate(prompts(args.batch, args.prompt_len), max_tokens=n_e2e,
+                   on_token=lambda r, t: stamps.append(time.perf_counter()) if r == args.batch - 1 else None)
+        # stamps[i] is taken after every sequence's i-th token reached the host
+        e2e_value = args.batch * args.steps / (stamps[-1] - stamps[-1 - args.steps])
+        e2e = {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
+               "d2h_bytes_per_step": 8 * args.batch}
 
     out = {
         "metric": "decode tokens/s (Llama-3.1-8B shape, batch 8, after 512-token prompts)",
@@ -223,25 +249,7 @@ def main() -> int:
             ms_b, _, _ = time_decode(b, max(8, args.steps // 2))
             points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 2)
         out["points"] = points
-        # prefill of 2,048 tokens
-        T = 2048
-        times = []
-        for i in range(warmup + 5):
-            s = eng.acquire()
-            p = prompts(1, T)[0]
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            eng.step([StepEntry(s, p, [T - 1])])
-            e1.record()
-            torch.cuda.synchronize()
-            eng.release(s)
-            if i >= warmup:
-                times.append(e0.elapsed_time(e1))
-        ms_p = sorted(times)[len(times) // 2]
-        fl = prefill_flops(cfg, args.layers, T)
-        out["prefill"] = {"value": round(T * 1000.0 / ms_p, 1), "tokens": T, "ms": round(ms_p, 3),
-                          "frac": round(fl / (ms_p * 1e-3) / (bf16_tflops * 1e12), 4)}
+        out["prefill"] = time_prefill()
     from mdma_b200 import ops_tensor
     ops_tensor.check_status(eng.device)
     print(json.dumps(out))
