@@ -1,0 +1,337 @@
+// Prefill attention on the fifth-generation tensor cores (bfloat16, paged cache,
+// causal, optional window, grouped-query).
+//
+// A block owns 128 query rows of one kv head of one sequence: the rows are
+// (token, query head of the group) pairs, token-major, so the G heads that share
+// a kv head share its key and value tiles.  Per 64-key block (one cache page):
+//     S = Q K^T        tcgen05.mma, M=128, N=64, operands from shared memory (TMA, 128-byte swizzle),
+//                      accumulator in tensor memory (two S buffers)
+//     softmax          128 threads, one query row each: tcgen05.ld of the row, mask, running maximum and
+//                      sum in float, P rounded to bfloat16 and written to shared memory in the operand layout
+//     O_blk = P V      tcgen05.mma, M=128, N=head_dim, V taken MN-major straight from the cache tile
+//     O += O_blk       each thread folds its row of O_blk (tensor memory, two buffers) into registers,
+//                      rescaled by the change of its maximum
+// Roles: warp 0 issues TMA loads (Q once, K/V through a ring), warp 1 issues the MMAs (S of block b+1 is
+// issued before P V of block b, so the tensor pipe works under the softmax), warps 2-5 are the softmax
+// rows.  Every wait is bounded.
+// Limits: head_dim a multiple of 16 up to 128, group size up to 128, page size a multiple of 64.
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace mdma {
+
+constexpr int kTcRows = 128, kTcKeys = 64, kTcThreadsA = 192, kKvStages = 3;
+
+struct AttnTcParams {
+    const int* seq_start; const int* seq_pos0; const int* seq_slot;
+    const int* page_table; int max_pages; int page_size;
+    __nv_bfloat16* out;
+    int n_heads, n_kv_heads, head_dim, group, tile_tokens, window, n_tokens;
+    float scale_log2;
+    int* status;
+};
+
+// shared memory map (bytes), all tiles 1024-aligned:
+//   Q: 2 halves x [128 rows x 128 B]           32 KB
+//   K ring: stages x 2 halves x [64 x 128 B]   stages x 16 KB
+//   V ring: same
+//   P: 2 buffers x [128 rows x 128 B]          32 KB
+constexpr int kQHalf = kTcRows * 128, kKvHalf = kTcKeys * 128, kPBuf = kTcRows * 128;
+constexpr int kSmemQ = 0, kSmemK = 2 * kQHalf, kSmemV = kSmemK + kKvStages * 2 * kKvHalf,
+              kSmemP = kSmemV + kKvStages * 2 * kKvHalf, kSmemBars = kSmemP + 2 * kPBuf,
+              kAttnTcSmem = kSmemBars + 256 + 1024;
+
+__global__ void __launch_bounds__(kTcThreadsA)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - ptx::smem_addr(smem_raw));
+    const uint32_t bars = base + kSmemBars;
+    // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], p_ready[2], o_full[2]
+    const uint32_t q_full = bars;
+    auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto kv_empty = [&](int s) { return bars + 8u * (1 + kKvStages + s); };
+    auto s_full = [&](int i) { return bars + 8u * (1 + 2 * kKvStages + i); };
+    auto p_ready = [&](int i) { return bars + 8u * (3 + 2 * kKvStages + i); };
+    auto o_full = [&](int i) { return bars + 8u * (5 + 2 * kKvStages + i); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + kSmemBars + 8 * (7 + 2 * kKvStages));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kSmemBars + 8 * (8 + 2 * kKvStages));
+
+    chain_release();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.y, kvh = blockIdx.z;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(q_full, 1);
+        for (int s = 0; s < kKvStages; ++s) { ptx::mbar_init(kv_full(s), 1); ptx::mbar_init(kv_empty(s), 1); }
+        for (int i = 0; i < 2; ++i) { ptx::mbar_init(s_full(i), 1); ptx::mbar_init(p_ready(i), 128); ptx::mbar_init(o_full(i), 1); }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) { ptx::tmem_alloc(ptx::smem_addr((const void*)tmem_slot), 512); ptx::tmem_relinquish(); }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;     // S: 2 x 64 columns, O: 2 x 128 columns
+
+    chain_wait();
+    const int row0_seq = p.seq_start[seq];
+    const int n_new = p.seq_start[seq + 1] - row0_seq;
+    const int tok0 = blockIdx.x * p.tile_tokens;
+    const bool active = tok0 < n_new;                 // uniform over the block
+    const int n_tok = active ? min(p.tile_tokens, n_new - tok0) : 0;
+    const int pos0 = p.seq_pos0[seq] + tok0;
+    const int last_pos = pos0 + n_tok - 1;
+    const int D = p.head_dim, G = p.group;
+    const int first_key = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;
+    const int b0 = first_key / kTcKeys, b1 = active ? last_pos / kTcKeys + 1 : b0;
+    const int nb = b1 - b0;
+    const int halves = (D + 63) / 64;
+
+    if (active && warp == 0 && lane == 0) {
+        // ---- TMA producer ---------------------------------------------------------
+        const int* pages = p.page_table + (size_t)p.seq_slot[seq] * p.max_pages;
+        ptx::mbar_expect_tx(q_full, halves * G * p.tile_tokens * 128);      // the box is G x tile_tokens rows of 128 bytes
+        for (int h = 0; h < halves; ++h)
+            ptx::tma_load_4d(base + kSmemQ + h * kQHalf, &map_q, q_full, h * 64, kvh * G, row0_seq + tok0, 0);
+        for (int i = 0; i < nb; ++i) {
+            const int s = i % kKvStages;
+            if (!ptx::mbar_wait(kv_empty(s), ((i / kKvStages) & 1) ^ 1, abort_flag)) break;
+            const int key0 = (b0 + i) * kTcKeys;
+            const int page = pages[key0 / p.page_size], row = key0 % p.page_size;
+            ptx::mbar_expect_tx(kv_full(s), 2 * halves * kKvHalf);
+            for (int h = 0; h < halves; ++h) {
+                ptx::tma_load_4d(base + kSmemK + (s * 2 + h) * kKvHalf, &map_k, kv_full(s), h * 64, kvh, row, page);
+                ptx::tma_load_4d(base + kSmemV + (s * 2 + h) * kKvHalf, &map_v, kv_full(s), h * 64, kvh, row, page);
+            }
+        }
+    } else if (active && warp == 1 && lane == 0) {
+        // ---- MMA issuer -------------------------------------------------------------
+        const uint32_t idesc_s = ptx::idesc_bf16_f32_ex(kTcRows, kTcKeys, 0);
+        const uint32_t idesc_o = ptx::idesc_bf16_f32_ex(kTcRows, D, 1);
+        auto issue_s = [&](int i) {        // S[i%2] = Q K(i)^T
+            const int s = i % kKvStages;
+            for (int kd = 0; kd < D / 16; ++kd) {
+                const uint32_t qa = base + kSmemQ + (kd / 4) * kQHalf + (kd % 4) * 32;
+                const uint32_t kb = base + kSmemK + (s * 2 + kd / 4) * kKvHalf + (kd % 4) * 32;
+                ptx::mma_bf16_ss(tmem_s + (i & 1) * 64, ptx::smem_desc_sw128(qa), ptx::smem_desc_sw128(kb), idesc_s, kd > 0);
+            }
+            ptx::mma_commit(s_full(i & 1));
+        };
+        bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
+        if (ok && nb > 0) ok = ptx::mbar_wait(kv_full(0), 0, abort_flag);
+        if (ok && nb > 0) { ptx::tc_fence_after_sync(); issue_s(0); }
+        for (int i = 0; i < nb && ok; ++i) {
+            if (i + 1 < nb) {
+                ok = ptx::mbar_wait(kv_full((i + 1) % kKvStages), ((i + 1) / kKvStages) & 1, abort_flag);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                issue_s(i + 1);
+            }
+            ok = ptx::mbar_wait(p_ready(i & 1), (i >> 1) & 1, abort_flag);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const int s = i % kKvStages;
+            for (int kk = 0; kk < kTcKeys / 16; ++kk) {     // O[i%2] = P(i) V(i): K dimension = keys
+                const uint32_t pa = base + kSmemP + (i & 1) * kPBuf + kk * 32;
+                const uint32_t vb = base + kSmemV + (s * 2) * kKvHalf + kk * 16 * 128;
+                ptx::mma_bf16_ss(tmem_o + (i & 1) * 128, ptx::smem_desc_sw128(pa),
+                                 ptx::smem_desc_sw128_mn(vb, kKvHalf), idesc_o, kk > 0);
+            }
+            ptx::mma_commit(o_full(i & 1));
+            ptx::mma_commit(kv_empty(s));
+        }
+    } else if (active && warp >= 2) {
+        // ---- softmax: one query row per thread ---------------------------------------
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;                       // row of the tile = TMEM lane
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const int t = r / G, g = r % G;
+        const bool row_valid = t < n_tok;
+        const int pos = pos0 + (row_valid ? t : n_tok - 1);
+        const int win = p.window > 0 ? pos + 1 - p.window : 0;
+        float o[128];
+#pragma unroll
+        for (int d = 0; d < 128; ++d) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+        uint8_t* p_rows = base_ptr + kSmemP + (size_t)r * 128;
+        bool ok = true;
+        auto fold = [&](int i, float corr) {                 // o = o * corr + O_blk(i)
+            ok = ptx::mbar_wait(o_full(i & 1), (i >> 1) & 1, abort_flag);
+            if (!ok) return;
+            ptx::tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (c * 32 < D) {
+                    float v[32];
+                    ptx::tmem_load_32_nowait(tmem_o + (i & 1) * 128 + lane_base + c * 32, v);
+                    ptx::tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * corr + v[j];
+                }
+            }
+            ptx::tc_fence_before_sync();
+        };
+        for (int i = 0; i < nb && ok; ++i) {
+            ok = ptx::mbar_wait(s_full(i & 1), (i >> 1) & 1, abort_flag);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            float sv[64];
+            ptx::tmem_load_32_nowait(tmem_s + (i & 1) * 64 + lane_base, sv);
+            ptx::tmem_load_32_nowait(tmem_s + (i & 1) * 64 + lane_base + 32, sv + 32);
+            ptx::tmem_load_wait();
+            const int key0 = (b0 + i) * kTcKeys;
+            const bool need_mask = key0 + kTcKeys - 1 > pos || key0 < win;
+            float mx = m;
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+                float v = sv[j] * p.scale_log2;
+                if (need_mask && (key0 + j > pos || key0 + j < win)) v = -INFINITY;
+                sv[j] = v;
+                mx = fmaxf(mx, v);
+            }
+            const float ref = mx == -INFINITY ? 0.f : mx;
+            const float corr = exp2f(m - ref);
+            m = mx;
+            float sum = 0.f;
+            // P row: 64 bf16 = 8 chunks of 16 bytes, chunk c at position c ^ (row & 7)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float p0 = exp2f(sv[c * 8 + 2 * j] - ref), p1 = exp2f(sv[c * 8 + 2 * j + 1] - ref);
+                    sum += p0 + p1;
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                    w[j] = *reinterpret_cast<uint32_t*>(&pk);
+                }
+                *reinterpret_cast<uint4*>(p_rows + (size_t)(i & 1) * kPBuf + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l = l * corr + sum;
+            ptx::fence_proxy_async_shared();
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(p_ready(i & 1));
+            if (i > 0) fold(i - 1, corr_prev);
+            corr_prev = corr;
+        }
+        if (ok && nb > 0) fold(nb - 1, corr_prev);
+        if (ok && row_valid && nb > 0) {
+            const float inv = 1.0f / l;
+            __nv_bfloat16* dst = p.out + ((size_t)(row0_seq + tok0 + t) * p.n_heads + kvh * G + g) * D;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                if (c * 8 < D) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        __nv_bfloat162 pk = __floats2bfloat162_rn(o[c * 8 + 2 * j] * inv, o[c * 8 + 2 * j + 1] * inv);
+                        w[j] = *reinterpret_cast<uint32_t*>(&pk);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) { ptx::tc_fence_after_sync(); ptx::tmem_dealloc(tmem_base, 512); }
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 2);
+}
+
+// ---- tensor maps -----------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn attn_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+// A bf16 tensor [d3][d2][d1][d0] (d0 innermost) with byte strides s1..s3, box (64, b1, b2, 1), 128-byte swizzle.
+static int make_map_4d(CUtensorMap* out, const void* ptr, const uint64_t dims[4], const uint64_t strides[3],
+                       const uint32_t box[4]) {
+    EncodeTiledFn fn = attn_encode_fn();
+    if (!fn) return fail("attention_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+    cuuint64_t s[3] = {strides[0], strides[1], strides[2]};
+    cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
+    cuuint32_t e[4] = {1, 1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), d, s, b, e,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail("attention_tc: cuTensorMapEncodeTiled failed with %d (dims %llu %llu %llu %llu)", (int)r,
+                    (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2], (unsigned long long)dims[3]);
+    return 0;
+}
+
+}  // namespace mdma
+
+using namespace mdma;
+
+extern "C" {
+
+int mdma_attention_tc_supported(int n_heads, int n_kv_heads, int head_dim, int page_size) {
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
+    const int g = n_heads / n_kv_heads;
+    return (head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128 && g <= kTcRows && page_size % kTcKeys == 0) ? 1 : 0;
+}
+
+// q: rows of the fused projection [tokens_cap, row_width], queries first; caches [pages, page_size, kv_heads, head_dim].
+int mdma_attention_tc(const void* q, int q_stride, int q_rows_cap, const void* k_cache, const void* v_cache,
+                      int n_pages, const int* seq_start, const int* seq_pos0, const int* seq_slot,
+                      const int* page_table, int max_pages, int page_size, void* out, int n_tokens, int n_seqs,
+                      int max_new, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                      int* status, cudaStream_t stream) {
+    MDMA_REQUIRE(mdma_attention_tc_supported(n_heads, n_kv_heads, head_dim, page_size),
+                 "attention_tc: heads %d / kv heads %d / head_dim %d / page %d is outside its limits", n_heads, n_kv_heads, head_dim, page_size);
+    MDMA_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0, "attention_tc: query rows must be 16-byte aligned");
+    MDMA_REQUIRE(n_seqs <= 65535 && n_kv_heads <= 65535, "attention_tc: grid too large");
+    if (n_tokens == 0 || n_seqs == 0) return 0;
+    const int G = n_heads / n_kv_heads;
+    AttnTcParams p;
+    p.seq_start = seq_start; p.seq_pos0 = seq_pos0; p.seq_slot = seq_slot;
+    p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size;
+    p.out = (__nv_bfloat16*)out; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
+    p.group = G; p.tile_tokens = kTcRows / G; p.window = window; p.n_tokens = n_tokens;
+    p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    CUtensorMap mq, mk, mv;
+    {   // queries: [tokens][heads][head_dim] inside rows of q_stride elements; box = 64 x G x tile_tokens
+        const uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)n_heads, (uint64_t)n_tokens, 1};
+        const uint64_t strides[3] = {(uint64_t)head_dim * 2, (uint64_t)q_stride * 2, (uint64_t)q_stride * 2 * (uint64_t)q_rows_cap};
+        const uint32_t box[4] = {64, (uint32_t)G, (uint32_t)p.tile_tokens, 1};
+        if (int rc = make_map_4d(&mq, q, dims, strides, box)) return rc;
+    }
+    {
+        const uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)n_kv_heads, (uint64_t)page_size, (uint64_t)n_pages};
+        const uint64_t strides[3] = {(uint64_t)head_dim * 2, (uint64_t)n_kv_heads * head_dim * 2,
+                                     (uint64_t)page_size * n_kv_heads * head_dim * 2};
+        const uint32_t box[4] = {64, 1, (uint32_t)kTcKeys, 1};
+        if (int rc = make_map_4d(&mk, k_cache, dims, strides, box)) return rc;
+        if (int rc = make_map_4d(&mv, v_cache, dims, strides, box)) return rc;
+    }
+    static bool once = false;
+    if (!once) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnTcSmem);
+        if (e != cudaSuccess) return fail("attention_tc: cannot reserve %d bytes of shared memory: %s", kAttnTcSmem, cudaGetErrorString(e));
+        once = true;
+    }
+    dim3 grid((max_new + p.tile_tokens - 1) / p.tile_tokens, n_seqs, n_kv_heads);
+    cudaError_t e = launch_chained(attention_tc_kernel, grid, dim3(kTcThreadsA), kAttnTcSmem, stream, mq, mk, mv, p);
+    if (e != cudaSuccess) return fail("attention_tc: launch failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+}  // extern "C"

@@ -148,9 +148,35 @@ def attention_splits(n_seqs: int, max_new: int, max_len: int, n_heads: int, n_kv
     return max(1, min(-(-2 * sms // blocks), key_blocks, 32))
 
 
+def attention_tc_supported(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    return (attention_supported(n_heads, n_kv_heads, head_dim) and n_heads // n_kv_heads <= 128
+            and page_size % 64 == 0)
+
+
 def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-              window: int, scale: float, splits: Optional[int] = None) -> None:
-    """Causal grouped-query attention of the step's tokens over the paged cache (bfloat16)."""
+              window: int, scale: float, splits: Optional[int] = None, impl: Optional[str] = None) -> None:
+    """Causal grouped-query attention of the step's tokens over the paged cache (bfloat16).
+    Steps that bring many tokens per sequence run on the tcgen05 kernel, single tokens on the
+    decode kernel, what is between (or outside the tcgen05 kernel's limits) on the mma.sync kernel;
+    `impl` ("tc" or "mma") forces one."""
+    group = n_heads // n_kv_heads
+    if impl is None:
+        impl = "tc" if (ctx.max_new * group > 64 and splits is None
+                        and attention_tc_supported(n_heads, n_kv_heads, head_dim, view.page_size)) else "mma"
+    if impl == "tc":
+        _need_cuda(qkv, view.k, view.v, out, view.page_table)
+        if qkv.dtype != torch.bfloat16 or view.k.dtype != torch.bfloat16:
+            raise KernelError("the tensor-core attention takes bfloat16")
+        assert qkv.stride(1) == 1 and out.is_contiguous() and out.shape[1] == n_heads * head_dim
+        assert view.k.is_contiguous() and view.v.is_contiguous()
+        st = _device_state(qkv.device)
+        flush_pending(qkv.device)
+        _call("tensor", "mdma_attention_tc", _ptr(qkv), _i(qkv.stride(0)), _i(qkv.shape[0]), _ptr(view.k),
+              _ptr(view.v), _i(view.k.shape[0]), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot),
+              _ptr(view.page_table), _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens),
+              _i(ctx.n_seqs), _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale),
+              _ptr(st["status"]), _stream())
+        return
     _need_cuda(qkv, view.k, view.v, out, view.page_table)
     if qkv.dtype != torch.bfloat16 or view.k.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention takes bfloat16")

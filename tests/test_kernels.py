@@ -246,13 +246,15 @@ class StepMeta:
 
 @pytest.mark.parametrize("H,K,hd,window", [(8, 2, 128, 0), (6, 2, 48, 0), (4, 4, 16, 0), (12, 2, 64, 0),
                                            (6, 1, 80, 0), (8, 2, 128, 100), (5, 5, 112, 33), (32, 8, 128, 0)])
-@pytest.mark.parametrize("case", ["prefill", "chunked", "decode", "decode_split"])
+@pytest.mark.parametrize("case", ["prefill", "chunked", "decode", "decode_split", "prefill_tc", "chunked_tc"])
 def test_attention_tensor(H, K, hd, window, case):
     """The tensor-core attention against the float64 statement of the reference's loop:
     whole prompts, prompts on top of a cached prefix, single tokens, and keys split over blocks."""
     from mdma_b200 import ops_tensor
     torch.manual_seed(H * 1000 + hd)
     page = 64
+    impl = "tc" if case.endswith("_tc") else "mma"
+    case = case.replace("_tc", "")
     if case == "prefill":
         cached, new = [0, 0, 0], [150, 3, 65]
     elif case == "chunked":
@@ -271,8 +273,9 @@ def test_attention_tensor(H, K, hd, window, case):
         pass
     view = View()
     view.k, view.v, view.page_table, view.max_pages, view.page_size = kc, vc, table, max_pages, page
-    splits = {"decode_split": 5, "chunked": 2}.get(case)
-    ops_tensor.attention(meta, q, view, out, H, K, hd, window, scale, splits=splits)
+    splits = {"decode_split": 5, "chunked": 2}.get(case) if impl == "mma" else None
+    ops_tensor.attention(meta, q, view, out, H, K, hd, window, scale, splits=splits, impl=impl)
+    ops_tensor.check_status(torch.device(DEV))
     want = reference_attention(q[:, :H * hd].double().cpu().reshape(T, H, hd), dense, meta.tok_seq, meta.tok_pos,
                                scale, window)
     close(out[:T], want, 2e-2, 2e-2)
