@@ -36,6 +36,7 @@ struct TcParams {
     int n_tokens, n_features, k_blocks, kb_per_split;
     float* partial;            // [splits, n_tokens, n_features] when MODE == kTcPartial
     int* status;               // device word set non-zero when a wait ran out
+    int cluster;               // > 1: that many blocks of a cluster split K and reduce through shared memory
 };
 
 template <int BN, int MODE>
@@ -70,9 +71,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int f0 = blockIdx.x * kBM;
+    // With a cluster, the blocks of a cluster share one output tile and divide its K range by rank.
+    const int rank = p.cluster > 1 ? (int)ptx::cluster_rank() : 0;
+    const int f0 = (blockIdx.x / p.cluster) * kBM;
     const int t0 = blockIdx.y * BN;
-    const int kb_begin = blockIdx.z * p.kb_per_split;
+    const int kb_begin = (p.cluster > 1 ? rank : (int)blockIdx.z) * p.kb_per_split;
     const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
     const int n_kb = kb_end - kb_begin;
 
@@ -150,45 +153,90 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             ptx::mma_commit(empty_bar(s));      // the stage is free once these MMAs have read it
         }
         ptx::mma_commit(acc_bar);               // the accumulator is complete
-    } else if (warp >= 2) {
-        // ---- epilogue: TMEM -> registers -> global ----------------------------
-        const int quad = warp & 3;              // the TMEM lanes this warp may read
-        const int f = f0 + quad * 32 + lane;
+    }
+    // ---- epilogue: TMEM -> registers -> (cluster reduction) -> global ------------------
+    const int quad = warp & 3;                  // the TMEM lanes an epilogue warp may read
+    const int f = f0 + quad * 32 + lane;
+    bool acc_ok = false;
+    if (warp >= 2) {
         chain_wait();                           // the output may still be read by an earlier kernel
-        const bool ok = ptx::mbar_wait(acc_bar, 0, abort_flag);
+        acc_ok = ptx::mbar_wait(acc_bar, 0, abort_flag) && n_kb > 0;
         ptx::tc_fence_after_sync();
-        if (ok && n_kb > 0) {
+    }
+    constexpr int kAccs = kDual ? 2 : 1;
+    if (p.cluster > 1) {
+        // Everyone's MMAs are done, so the leader's stage ring is free: the other ranks write their
+        // accumulators there ([rank-1][accumulator][column][128 features] floats), the leader adds
+        // them to its own in rank order.
+        ptx::cluster_sync();
+        if (warp >= 2 && rank > 0) {
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            const uint32_t slot = ptx::cluster_map(base, 0) +
+                                  (uint32_t)(((rank - 1) * kAccs * BN) * kBM + quad * 32 + lane) * 4u;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
-                if (t0 + c >= p.n_tokens) break;           // uniform over the warp
+                if (t0 + c >= p.n_tokens) break;
                 float v[16], u[16];
+                if (acc_ok) {
+                    ptx::tmem_load_16(lane_addr + c, v);
+                    if (kDual) ptx::tmem_load_16(lane_addr + BN + c, u);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) { v[j] = 0.f; u[j] = 0.f; }
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    ptx::cluster_store_f32(slot + (uint32_t)((c + j) * kBM) * 4u, v[j]);
+                    if (kDual) ptx::cluster_store_f32(slot + (uint32_t)((BN + c + j) * kBM) * 4u, u[j]);
+                }
+            }
+        }
+        ptx::cluster_sync();
+    }
+    if (warp >= 2 && rank == 0 && (acc_ok || p.cluster > 1)) {
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const float* staged = reinterpret_cast<const float*>(base_ptr) + quad * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+            if (t0 + c >= p.n_tokens) break;           // uniform over the warp
+            float v[16], u[16];
+            if (acc_ok) {
                 ptx::tmem_load_16(lane_addr + c, v);
                 if (kDual) ptx::tmem_load_16(lane_addr + BN + c, u);
-                if (f < p.n_features) {
-                    const int valid = min(16, p.n_tokens - (t0 + c));
-                    if (MODE == kTcAccumulate) {
-                        // read the 16 residual values first so the loads overlap, then add and store
-                        float* o = reinterpret_cast<float*>(p.out) + (size_t)(t0 + c) * p.ldo + f;
-                        float old[16];
+            } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) old[j] = j < valid ? o[(size_t)j * p.ldo] : 0.f;
+                for (int j = 0; j < 16; ++j) { v[j] = 0.f; u[j] = 0.f; }
+            }
+            for (int r = 1; r < p.cluster; ++r) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) if (j < valid) o[(size_t)j * p.ldo] = old[j] + v[j];
-                    } else {
+                for (int j = 0; j < 16; ++j) {
+                    v[j] += staged[(size_t)(((r - 1) * kAccs * BN) + c + j) * kBM];
+                    if (kDual) u[j] += staged[(size_t)(((r - 1) * kAccs * BN) + BN + c + j) * kBM];
+                }
+            }
+            if (f < p.n_features) {
+                const int valid = min(16, p.n_tokens - (t0 + c));
+                if (MODE == kTcAccumulate) {
+                    // read the 16 residual values first so the loads overlap, then add and store
+                    float* o = reinterpret_cast<float*>(p.out) + (size_t)(t0 + c) * p.ldo + f;
+                    float old[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (j >= valid) break;
-                            const int t = t0 + c + j;
-                            float r = v[j];
-                            if (MODE == kTcSwiGLU) r = r / (1.0f + __expf(-r)) * u[j];
-                            if (MODE == kTcPartial) {
-                                p.partial[((size_t)blockIdx.z * p.n_tokens + t) * p.n_features + f] = r;
-                            } else if (p.out_f32) {
-                                reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + f] = r;
-                            } else {
-                                reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(r);
-                            }
+                    for (int j = 0; j < 16; ++j) old[j] = j < valid ? o[(size_t)j * p.ldo] : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) if (j < valid) o[(size_t)j * p.ldo] = old[j] + v[j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j >= valid) break;
+                        const int t = t0 + c + j;
+                        float r = v[j];
+                        if (MODE == kTcSwiGLU) r = r / (1.0f + __expf(-r)) * u[j];
+                        if (MODE == kTcPartial) {
+                            p.partial[((size_t)blockIdx.z * p.n_tokens + t) * p.n_features + f] = r;
+                        } else if (p.out_f32) {
+                            reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + f] = r;
+                        } else {
+                            reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(r);
                         }
                     }
                 }
@@ -298,6 +346,25 @@ static int run_tc(const void* x, int ldx, const void* w, const void* w2, int K, 
     if (MODE == kTcSwiGLU)
         if (int rc = make_map_2d(&mw2, w2, (uint64_t)p.n_features, (uint64_t)K, (uint64_t)K * 2, kBM)) return rc;
     if (int rc = make_map_2d(&mx, x, (uint64_t)p.n_tokens, (uint64_t)K, (uint64_t)ldx * 2, BN)) return rc;
+    // the staging of the cluster reduction must fit the stage ring: shrink the cluster until it does
+    while (p.cluster > 1 && (p.cluster - 1) * (MODE == kTcSwiGLU ? 2 : 1) * BN * kBM * 4 > S::kStages * S::kStage) {
+        --p.cluster;
+        p.kb_per_split = (p.k_blocks + p.cluster - 1) / p.cluster;
+    }
+    if (p.cluster > 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(((p.n_features + kBM - 1) / kBM) * p.cluster, (p.n_tokens + BN - 1) / BN, 1);
+        cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = S::kBytes; cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = p.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = chaining_enabled() ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, MODE>, mw, mw2, mx, p);
+        if (e != cudaSuccess) return fail("gemm_tc: cluster launch failed: %s", cudaGetErrorString(e));
+        return 0;
+    }
     dim3 grid((p.n_features + kBM - 1) / kBM, (p.n_tokens + BN - 1) / BN, splits);
     launch_chained(gemm_tc_kernel<BN, MODE>, grid, dim3(kTcThreads), S::kBytes, stream, mw, mw2, mx, p);
     MDMA_LAUNCH_OK("gemm_tc");
@@ -326,12 +393,19 @@ int mdma_gemm_tc_supported(int n_features, int K) { return (K % 8 == 0 && K >= 8
 
 // Bytes of float scratch a call with these sizes needs (0 when it does not split K).
 // `splits` <= 0 asks the library to choose.
+// `splits_out` < 0 means: split K that many ways inside a cluster (no scratch, reduced in shared memory).
 int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_count, int* bn_out, int* splits_out) {
     int bn = 16;
     while (bn < 256 && bn < n_tokens) bn *= 2;
     const int k_blocks = (K + kBK - 1) / kBK;
     const long tiles = (long)((n_features + kBM - 1) / kBM) * ((n_tokens + bn - 1) / bn);
     int splits = 1;
+    if (mode == kTcSwiGLU && bn <= 64 && tiles < sm_count && k_blocks >= 8) {
+        // The SwiGLU ending needs complete sums, so its K split stays inside a cluster of two blocks
+        // (measured at batch 8: 37.4 us against 41.8 us unsplit; larger clusters and cluster splits
+        // of the other products were slower than partial sums through global memory).
+        *bn_out = bn; *splits_out = -2; return 0;
+    }
     if (mode != kTcSwiGLU && tiles < sm_count) {
         splits = (int)((sm_count + tiles - 1) / tiles);
         if (splits > 16) splits = 16;
@@ -376,6 +450,20 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     MDMA_REQUIRE((n_tokens + bn - 1) / bn <= 65535, "gemm_tc: too many token tiles");
     if (n_tokens == 0) return 0;
     const int k_blocks = (K + kBK - 1) / kBK;
+    if (splits < -1) {
+        // K split inside a cluster
+        int c = -splits;
+        MDMA_REQUIRE(c <= 8, "gemm_tc: clusters of more than 8 blocks are not portable");
+        if (c > k_blocks) c = k_blocks;
+        TcParams pc;
+        pc.out = out; pc.ldo = ldo; pc.out_f32 = out_f32;
+        pc.n_tokens = n_tokens; pc.n_features = n_features; pc.k_blocks = k_blocks;
+        pc.kb_per_split = (k_blocks + c - 1) / c;
+        pc.partial = nullptr; pc.status = status; pc.cluster = c;
+        if (mode == kTcStore) return run_tc_bn<kTcStore>(bn, x, ldx, w, w2, K, pc, 1, stream);
+        if (mode == kTcAccumulate) return run_tc_bn<kTcAccumulate>(bn, x, ldx, w, w2, K, pc, 1, stream);
+        return run_tc_bn<kTcSwiGLU>(bn, x, ldx, w, w2, K, pc, 1, stream);
+    }
     if (splits < 1) splits = 1;
     if (splits > k_blocks) splits = k_blocks;
     if (mode == kTcSwiGLU) splits = 1;
@@ -384,7 +472,7 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     p.n_tokens = n_tokens; p.n_features = n_features; p.k_blocks = k_blocks;
     p.kb_per_split = (k_blocks + splits - 1) / splits;
     splits = (k_blocks + p.kb_per_split - 1) / p.kb_per_split;     // no empty split
-    p.partial = nullptr; p.status = status;
+    p.partial = nullptr; p.status = status; p.cluster = 1;
     if (splits == 1) {
         if (mode == kTcStore) return run_tc_bn<kTcStore>(bn, x, ldx, w, w2, K, p, 1, stream);
         if (mode == kTcAccumulate) return run_tc_bn<kTcAccumulate>(bn, x, ldx, w, w2, K, p, 1, stream);

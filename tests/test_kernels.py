@@ -386,6 +386,34 @@ def test_gemm_tensor_split_k_is_reproducible(splits):
     ops_tensor.check_status(torch.device(DEV))
 
 
+@pytest.mark.parametrize("cluster", [2, 3, 8])
+@pytest.mark.parametrize("M,N,K,mode", [(8, 520, 2048, 0), (5, 300, 1024, 1), (17, 264, 1536, 2), (1, 128, 4096, 1)])
+def test_gemm_tensor_cluster_split(cluster, M, N, K, mode):
+    """K divided among the blocks of a cluster, summed through shared memory in rank order."""
+    from mdma_b200 import ops_tensor
+    ops = ops_mod()
+    torch.manual_seed(K + cluster)
+    a = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    w2 = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    ref = a.double() @ w.double().t()
+    outs = []
+    for _ in range(2):
+        if mode == 1:
+            out = torch.ones(M + 1, N, device=DEV)
+            ops_tensor.gemm(a, w, out, ops.GEMM_ACCUMULATE, None, M, splits=-cluster)
+            want = ref + 1.0
+        else:
+            out = torch.full((M + 1, N), 9.0, device=DEV, dtype=torch.float32 if mode == 0 else torch.bfloat16)
+            ops_tensor.gemm(a, w, out, mode, w2 if mode == 2 else None, M, splits=-cluster)
+            want = ref if mode == 0 else ref / (1 + torch.exp(-ref)) * (a.double() @ w2.double().t())
+        close(out[:M], want, 1e-4 if out.dtype == torch.float32 else 1e-2, 0 if out.dtype == torch.float32 else 1e-2)
+        assert bool((out[M:] == (1.0 if mode == 1 else 9.0)).all())
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    ops_tensor.check_status(torch.device(DEV))
+
+
 def test_gemm_tensor_refuses_what_it_cannot_do():
     from mdma_b200 import ops_tensor
     from mdma_b200.ops import KernelError
