@@ -122,6 +122,12 @@ def build(name: str, verbose: bool = True) -> str:
     if res.returncode != 0:
         raise BuildError(f"linking {name} failed:\n{res.stdout.decode(errors='replace')}")
     os.replace(tmp_out, out)      # atomic: concurrent builders end with one good file
+    for stale in os.listdir(bdir):      # older builds of this library
+        if stale.startswith(f"libmdma_{name}-") and stale.endswith(".so") and stale != os.path.basename(out):
+            try:
+                os.remove(os.path.join(bdir, stale))
+            except OSError:
+                pass
     say(f"built {os.path.basename(out)} in {time.time() - t0:.0f} s")
     return out
 
