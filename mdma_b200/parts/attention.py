@@ -64,7 +64,8 @@ class Attention(Part):
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.position.bind({}, rt)
+        if not self.position.tensor_specs():
+            self.position.bind({}, rt)      # a position part with tensors of its own is bound by the model
         if self.shared_cache:
             fused = tensors["q_proj.weight"]
         else:

@@ -165,3 +165,156 @@ def test_toy_architecture_builds_and_steps(tmp_path, dtype, tol):
             eng.release(slots[i])
         live = [i for i in live if pos[i] < len(seqs[i])]
     eng.cache.check()
+
+
+# ---------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, both defined here.
+
+def register_toy_routed():
+    from mdma_b200 import ops
+    from mdma_b200.config import Architecture
+    from mdma_b200.parts.base import Part
+    from mdma_b200.registry import ARCHITECTURES, FEED_FORWARDS, POSITIONS
+    from mdma_b200.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+
+    class RoutedMLP(Part):
+        """Top-1 of n experts: router logits in float32, the chosen expert's SwiGLU, weighted by
+        its softmax probability; x += p * expert(h)."""
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.width, self.inner, self.n = spec.params["width"], spec.params["inner"], spec.params["experts"]
+
+        def tensor_specs(self):
+            t = {"router.weight": TensorSpec((self.n, self.width))}
+            for e in range(self.n):
+                t[f"experts.{e}.gate.weight"] = TensorSpec((self.inner, self.width))
+                t[f"experts.{e}.up.weight"] = TensorSpec((self.inner, self.width))
+                t[f"experts.{e}.down.weight"] = TensorSpec((self.width, self.inner))
+            return t
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.t = {k: v.float() for k, v in tensors.items()}
+
+        def forward(self, ctx, h, x):
+            hf = h[:ctx.n_tokens].float()
+            probs = torch.softmax(hf @ self.t["router.weight"].t(), dim=-1)      # router in float32
+            top = probs.argmax(dim=-1)
+            for e in range(self.n):
+                rows = (top == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                he = hf[rows]
+                g = he @ self.t[f"experts.{e}.gate.weight"].t()
+                act = g / (1 + torch.exp(-g)) * (he @ self.t[f"experts.{e}.up.weight"].t())
+                x[rows] += probs[rows, e:e + 1] * (act @ self.t[f"experts.{e}.down.weight"].t())
+
+    class LearnedOffsets(Part):
+        """A position encoding that is no rotation: q and k get a learned vector per position added
+        (a table in the checkpoint), then k and v go to the cache."""
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.head_dim, self.max_pos = spec.params["head_dim"], spec.params["max_positions"]
+
+        def tensor_specs(self):
+            return {"table": TensorSpec((self.max_pos, self.head_dim))}
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.table = tensors["table"]
+            self.zero_freq = torch.zeros(self.head_dim // 2, dtype=torch.float32, device=rt.device)
+
+        def encode_and_store(self, ctx, qkv, n_heads, n_kv_heads, head_dim, view, write_kv):
+            n = ctx.n_tokens
+            add = self.table[ctx.tok_pos.long()].to(qkv.dtype)                    # [n, head_dim]
+            heads = n_heads + (n_kv_heads if write_kv else 0)                     # q and k, not v
+            rows = qkv[:n, :heads * head_dim].reshape(n, heads, head_dim)
+            rows += add[:, None, :]
+            # angle 0 everywhere: the library's cache-write kernel then only stores k and v
+            ops.rope_cache_write(qkv, n, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot, self.zero_freq,
+                                 view.k if write_kv else None, view.v if write_kv else None,
+                                 view.page_table if write_kv else None, view.max_pages, view.page_size,
+                                 n_heads, n_kv_heads, head_dim, head_dim, False, write_kv)
+
+    FEED_FORWARDS.register("toy_routed", RoutedMLP, replace=True)
+    POSITIONS.register("toy_learned", LearnedOffsets, replace=True)
+
+    def describe(c):
+        norm = lambda p: PartSpec("rmsnorm", dict(width=E, eps=c["eps"]), prefix=p)
+        pos = PartSpec("toy_learned", dict(head_dim=D, max_positions=64), prefix="pos.")
+        attn = lambda p: PartSpec("attention", dict(hidden_size=E, num_heads=H, num_kv_heads=K, head_dim=D,
+                                                    scale=D ** -0.5, window=0, position=pos), prefix=p)
+        layers = [
+            LayerSpec("prenorm", norm("l0.n1."), attn("l0.attn."), norm("l0.n2."),
+                      PartSpec("toy_routed", dict(width=E, inner=40, experts=3), prefix="l0.moe.")),
+            LayerSpec("prenorm", norm("l1.n1."), attn("l1.attn."), norm("l1.n2."),
+                      PartSpec("gated_mlp", dict(hidden_size=E, intermediate_size=F), prefix="l1.mlp.")),
+        ]
+        return ModelSpec(hidden_size=E, vocab_size=V, max_positions=64,
+                         embedding=PartSpec("embedding", dict(vocab_size=V, width=E), prefix="emb."),
+                         layers=layers, schedule=[ScheduleEntry(0), ScheduleEntry(1)], final_norm=norm("final."),
+                         lm_head=PartSpec("lm_head", dict(vocab_size=V, width=E), prefix="head."))
+
+    ARCHITECTURES.register("ToyRoutedLM", Architecture("ToyRoutedLM", dict, describe), replace=True)
+
+
+def plain_toy_routed(c, W, ids):
+    W = {k: v.double() for k, v in W.items()}
+    T = len(ids)
+    x = W["emb.weight"][torch.tensor(ids)]
+    add = W["pos.table"][:T]
+
+    def attn(x, p):
+        h = plain_rmsnorm(x, W[p + "n1.weight"], c["eps"])
+        q = (h @ W[p + "attn.q_proj.weight"].t()).reshape(T, H, D) + add[:, None, :]
+        k = (h @ W[p + "attn.k_proj.weight"].t()).reshape(T, K, D) + add[:, None, :]
+        v = (h @ W[p + "attn.v_proj.weight"].t()).reshape(T, K, D)
+        return x + plain_attention(q, k, v, D ** -0.5) @ W[p + "attn.o_proj.weight"].t()
+
+    x = attn(x, "l0.")
+    h = plain_rmsnorm(x, W["l0.n2.weight"], c["eps"])
+    probs = torch.softmax(h @ W["l0.moe.router.weight"].t(), dim=-1)
+    top = probs.argmax(-1)
+    out = x.clone()
+    for t in range(T):
+        e = int(top[t])
+        g = h[t] @ W[f"l0.moe.experts.{e}.gate.weight"].t()
+        act = plain_swiglu(g, h[t] @ W[f"l0.moe.experts.{e}.up.weight"].t())
+        out[t] = x[t] + probs[t, e] * (act @ W[f"l0.moe.experts.{e}.down.weight"].t())
+    x = attn(out, "l1.")
+    h = plain_rmsnorm(x, W["l1.n2.weight"], c["eps"])
+    x = x + plain_swiglu(h @ W["l1.mlp.gate_proj.weight"].t(), h @ W["l1.mlp.up_proj.weight"].t()) @ W["l1.mlp.down_proj.weight"].t()
+    return plain_rmsnorm(x, W["final.weight"], c["eps"]) @ W["head.weight"].t()
+
+
+def test_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """One model with a routed and a dense feed-forward in different layers and a position encoding that
+    is not rotary, registered from here; float32 so that every token takes the same expert in both."""
+    register_toy_routed()
+    from mdma_b200.engine import Engine, StepEntry
+    from mdma_b200.weights import write_random_model, write_safetensors
+    from mdma_b200.weights.safetensors_io import SafetensorsFile
+    cfg = dict(architectures=["ToyRoutedLM"], eps=1e-5)
+    d = write_random_model(str(tmp_path / "toy2"), cfg, 3, torch.float32)
+    sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    W = {n: sf.tensor(n).clone() for n in sf.entries}
+    W["l0.moe.router.weight"] = W["l0.moe.router.weight"] * 40      # decisive routing, all experts used
+    W["pos.table"] = W["pos.table"] * 10
+    write_safetensors(os.path.join(d, "model.safetensors"), W)
+    eng = Engine(d, dtype="float32", max_batch=2, max_context=64)
+    g = torch.Generator().manual_seed(1)
+    seqs = [torch.randint(0, V, (n,), generator=g).tolist() for n in (40, 13)]
+    ref = [plain_toy_routed(cfg, W, s).numpy() for s in seqs]
+    slots = [eng.acquire() for _ in seqs]
+    cut = [25, 5]
+    out = eng.step([StepEntry(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, seqs, cut)]).cpu().numpy()
+    off = 0
+    for s, r, c in zip(seqs, ref, cut):
+        assert np.abs(out[off:off + c] - r[:c]).max() < 5e-5
+        off += c
+    for step in range(8):
+        out = eng.step([StepEntry(sl, [s[c + step]], [0]) for sl, s, c in zip(slots, seqs, cut)]).cpu().numpy()
+        for row, (r, c) in enumerate(zip(ref, cut)):
+            assert np.abs(out[row] - r[c + step]).max() < 5e-5
