@@ -252,6 +252,155 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
 }
 
+// ---------------------------------------------------------------------------------------
+// The same product for many tokens with two blocks working as one (cta_group::2): a pair
+// covers 256 features x 256 tokens.  Each block loads its own 128 weight rows and only HALF
+// of the token tile (128 tokens) per stage; one tcgen05.mma issued by the leading block reads
+// both blocks' shared memory and writes 128 accumulator rows into each block's tensor memory.
+// Per block and K step that is 32 KB of operands instead of 48 KB (48 instead of 64 with two
+// weight matrices), which is what the single-block kernel runs short of.
+template <int MODE>
+struct Tc2Smem {
+    static constexpr int kA = kBM * kBK * 2, kB = 128 * kBK * 2;
+    static constexpr int kStage = kA * (MODE == kTcSwiGLU ? 2 : 1) + kB;
+    static constexpr int kStages = (200 * 1024) / kStage;
+    static constexpr int kBytes = kStages * kStage + 1024 + 256;
+    static constexpr int kTmemCols = MODE == kTcSwiGLU ? 512 : 256;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+                const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    using S = Tc2Smem<MODE>;
+    constexpr int kStages = S::kStages;
+    constexpr bool kDual = MODE == kTcSwiGLU;
+    constexpr int BN = 256;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - ptx::smem_addr(smem_raw));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + kStages * S::kStage);
+    const uint32_t bar0 = base + kStages * S::kStage;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+    const uint32_t acc_bar = bar0 + 8u * (2 * kStages);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)ptx::cluster_rank();
+    const int f0 = (blockIdx.x / 2) * 256 + rank * 128;        // this block's weight rows
+    const int t0 = blockIdx.y * BN;                             // the pair's tokens; this block loads t0 + rank*128 ...
+    const int n_kb = p.k_blocks;
+
+    // This kernel takes no part in programmatic dependent launch: launched early next to the tail of
+    // another kernel it stalled now and then (seen with the rotary, norm and attention kernels before
+    // it); it is used for many tokens, where a launch gap is nothing against its run time.
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+        ptx::mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_addr((const void*)tmem_slot), S::kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    ptx::cluster_sync();                   // both blocks' barriers exist before either signals the other
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: this block's halves; bytes are counted on the leading block's barrier ----
+        ptx::prefetch_tensormap(&map_w);
+        ptx::prefetch_tensormap(&map_x);
+        if (kDual) ptx::prefetch_tensormap(&map_w2);
+        int issued = 0;
+        for (int i = 0; i < n_kb; ++i) {
+            const int s = i % kStages;
+            if (!ptx::mbar_wait(empty_bar(s), ((i / kStages) & 1) ^ 1, abort_flag)) break;
+            const uint32_t stage = base + s * S::kStage;
+            const uint32_t lead_full = ptx::cluster_map(full_bar(s), 0);
+            if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 2 * S::kStage);       // both blocks' bytes
+            const int k = i * kBK;
+            ptx::tma_load_2d_pair(stage, &map_w, lead_full, k, f0);
+            if (kDual) ptx::tma_load_2d_pair(stage + S::kA, &map_w2, lead_full, k, f0);
+            ptx::tma_load_2d_pair(stage + S::kA * (kDual ? 2 : 1), &map_x, lead_full, k, t0 + rank * 128);
+            ++issued;
+        }
+        (void)issued;
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---- MMA issuer (leading block only) ----------------------------------------------
+        constexpr uint32_t idesc = ptx::idesc_bf16_f32(256, BN);
+        bool ok = true;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            const int s = i % kStages;
+            ok = ptx::mbar_wait(full_bar(s), (i / kStages) & 1, abort_flag);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t stage = base + s * S::kStage;
+            const uint32_t a_addr = stage, b_addr = stage + S::kA * (kDual ? 2 : 1);
+#pragma unroll
+            for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+                const uint64_t b_desc = ptx::smem_desc_sw128(b_addr + kk * kUmmaK * 2);
+                const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+                ptx::mma_bf16_ss_pair(tmem_base, ptx::smem_desc_sw128(a_addr + kk * kUmmaK * 2), b_desc, idesc, acc);
+                if (kDual)
+                    ptx::mma_bf16_ss_pair(tmem_base + BN, ptx::smem_desc_sw128(a_addr + S::kA + kk * kUmmaK * 2),
+                                          b_desc, idesc, acc);
+            }
+            ptx::mma_commit_pair(empty_bar(s), 3);      // frees the stage in both blocks
+        }
+        ptx::mma_commit_pair(acc_bar, 3);               // both blocks' accumulators are complete
+    }
+    if (warp >= 2) {
+        // ---- epilogue: each block stores its own 128 features x 256 tokens ---------------------
+        const int quad = warp & 3;
+        const int f = f0 + quad * 32 + lane;
+        const bool ok = ptx::mbar_wait(acc_bar, 0, abort_flag);
+        ptx::tc_fence_after_sync();
+        if (ok && n_kb > 0) {
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (t0 + c >= p.n_tokens) break;
+                float v[16], u[16];
+                ptx::tmem_load_16(lane_addr + c, v);
+                if (kDual) ptx::tmem_load_16(lane_addr + BN + c, u);
+                if (f < p.n_features) {
+                    const int valid = min(16, p.n_tokens - (t0 + c));
+                    if (MODE == kTcAccumulate) {
+                        float* o = reinterpret_cast<float*>(p.out) + (size_t)(t0 + c) * p.ldo + f;
+                        float old[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) old[j] = j < valid ? o[(size_t)j * p.ldo] : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (j < valid) o[(size_t)j * p.ldo] = old[j] + v[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (j >= valid) break;
+                            const int t = t0 + c + j;
+                            float r = v[j];
+                            if (MODE == kTcSwiGLU) r = r / (1.0f + __expf(-r)) * u[j];
+                            if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + f] = r;
+                            else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(r);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    ptx::tc_fence_before_sync();
+    ptx::cluster_sync();                   // neither block leaves (or frees tensor memory) while the other may still use it
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, S::kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 3);
+}
+
 // out (=, +=) sum over splits of partial, in split order.
 template <int MODE>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int n_tokens, int n_features,
@@ -372,6 +521,34 @@ static int run_tc(const void* x, int ldx, const void* w, const void* w2, int K, 
 }
 
 template <int MODE>
+static int run_tc2(const void* x, int ldx, const void* w, const void* w2, int K, TcParams p, cudaStream_t stream) {
+    using S = Tc2Smem<MODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+        if (e != cudaSuccess) return fail("gemm_tc2: cannot reserve %d bytes of shared memory: %s", S::kBytes, cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap mw, mw2, mx;
+    if (int rc = make_map_2d(&mw, w, (uint64_t)p.n_features, (uint64_t)K, (uint64_t)K * 2, kBM)) return rc;
+    mw2 = mw;
+    if (MODE == kTcSwiGLU)
+        if (int rc = make_map_2d(&mw2, w2, (uint64_t)p.n_features, (uint64_t)K, (uint64_t)K * 2, kBM)) return rc;
+    if (int rc = make_map_2d(&mx, x, (uint64_t)p.n_tokens, (uint64_t)K, (uint64_t)ldx * 2, 128)) return rc;
+    p.cluster = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(((p.n_features + 255) / 256) * 2, (p.n_tokens + 255) / 256, 1);
+    cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = S::kBytes; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mw2, mx, p);
+    if (e != cudaSuccess) return fail("gemm_tc2: launch failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+template <int MODE>
 static int run_tc_bn(int bn, const void* x, int ldx, const void* w, const void* w2, int K, const TcParams& p,
                      int splits, cudaStream_t stream) {
     switch (bn) {
@@ -395,6 +572,9 @@ int mdma_gemm_tc_supported(int n_features, int K) { return (K % 8 == 0 && K >= 8
 // `splits` <= 0 asks the library to choose.
 // `splits_out` < 0 means: split K that many ways inside a cluster (no scratch, reduced in shared memory).
 int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_count, int* bn_out, int* splits_out) {
+    if (n_tokens > 128) {      // many tokens: block pairs, 256 features x 256 tokens per pair (`bn` code 512)
+        *bn_out = 512; *splits_out = 1; return 0;
+    }
     int bn = 16;
     while (bn < 256 && bn < n_tokens) bn *= 2;
     const int k_blocks = (K + kBK - 1) / kBK;
@@ -449,7 +629,7 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     MDMA_REQUIRE(mode != kTcSwiGLU || w2, "gemm_tc: SwiGLU needs two weights");
     MDMA_REQUIRE(mode != kTcAccumulate || out_f32, "gemm_tc: the residual stream is float");
     MDMA_REQUIRE(mode >= 0 && mode <= 2, "gemm_tc: unknown mode %d", mode);
-    MDMA_REQUIRE((n_tokens + bn - 1) / bn <= 65535, "gemm_tc: too many token tiles");
+    MDMA_REQUIRE(bn == 512 || (n_tokens + bn - 1) / bn <= 65535, "gemm_tc: too many token tiles");
     if (n_tokens == 0) return 0;
     const int k_blocks = (K + kBK - 1) / kBK;
     if (splits < -1) {
@@ -475,6 +655,11 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     p.kb_per_split = (k_blocks + splits - 1) / splits;
     splits = (k_blocks + p.kb_per_split - 1) / p.kb_per_split;     // no empty split
     p.partial = nullptr; p.status = status; p.cluster = 1;
+    if (bn == 512) {           // the two-block kernel (a pair covers 256 features x 256 tokens)
+        if (mode == kTcStore) return run_tc2<kTcStore>(x, ldx, w, w2, K, p, stream);
+        if (mode == kTcAccumulate) return run_tc2<kTcAccumulate>(x, ldx, w, w2, K, p, stream);
+        return run_tc2<kTcSwiGLU>(x, ldx, w, w2, K, p, stream);
+    }
     if (splits == 1) {
         if (mode == kTcStore) return run_tc_bn<kTcStore>(bn, x, ldx, w, w2, K, p, 1, stream);
         if (mode == kTcAccumulate) return run_tc_bn<kTcAccumulate>(bn, x, ldx, w, w2, K, p, 1, stream);

@@ -4,6 +4,7 @@ a shape the kernels refuse raises `KernelError`."""
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -160,6 +161,8 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
     decode kernel, what is between (or outside the tcgen05 kernel's limits) on the mma.sync kernel;
     `impl` ("tc" or "mma") forces one."""
     group = n_heads // n_kv_heads
+    if impl is None and os.environ.get("MDMA_ATTN"):
+        impl = os.environ["MDMA_ATTN"]
     if impl is None:
         impl = "tc" if (ctx.max_new * group > 64 and splits is None
                         and attention_tc_supported(n_heads, n_kv_heads, head_dim, view.page_size)) else "mma"

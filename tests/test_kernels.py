@@ -414,6 +414,32 @@ def test_gemm_tensor_cluster_split(cluster, M, N, K, mode):
     ops_tensor.check_status(torch.device(DEV))
 
 
+@pytest.mark.parametrize("M,N,K,mode", [(256, 256, 64, 0), (300, 520, 1032, 0), (1000, 264, 512, 1), (257, 384, 640, 2),
+                                        (2048, 1024, 2048, 2), (130, 100, 72, 0)])
+def test_gemm_tensor_block_pairs(M, N, K, mode):
+    """The two-block kernel (cta_group::2): a pair covers 256 features x 256 tokens."""
+    from mdma_b200 import ops_tensor
+    ops = ops_mod()
+    torch.manual_seed(M + N)
+    a = (torch.randn(M + 2, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    w2 = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    ref = a[:M].double() @ w.double().t()
+    if mode == 1:
+        x = torch.randn(M + 2, N, device=DEV)
+        x0 = x.clone()
+        ops_tensor.gemm(a, w, x, ops.GEMM_ACCUMULATE, None, M, bn=512, splits=1)
+        close(x[:M], x0[:M].double() + ref, 2e-5 * max(K, 64) ** 0.5 + 1e-5)
+        assert torch.equal(x[M:], x0[M:])
+    else:
+        out = torch.full((M + 2, N), 9.0, device=DEV, dtype=torch.bfloat16)
+        ops_tensor.gemm(a, w, out, mode, w2 if mode == 2 else None, M, bn=512, splits=1)
+        want = ref if mode == 0 else ref / (1 + torch.exp(-ref)) * (a[:M].double() @ w2.double().t())
+        close(out[:M], want, 1e-2, 1e-2)
+        assert bool((out[M:] == 9.0).all())
+    ops_tensor.check_status(torch.device(DEV))
+
+
 def test_gemm_tensor_refuses_what_it_cannot_do():
     from mdma_b200 import ops_tensor
     from mdma_b200.ops import KernelError
