@@ -81,10 +81,9 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
 }
 
 // ------------------------------------------------- rotary + cache write
-// One block per (token, head) of the fused projection row
-// [q heads | k heads | v heads].  q is rotated in place; rotated k and raw v go
-// to the cache row of (slot, position): page page_table[slot][pos / page_size],
-// row pos % page_size of that page.
+// One block per token works on its fused projection row [q heads | k heads | v heads]:
+// q is rotated in place; rotated k and raw v go to the cache row of (slot, position):
+// page page_table[slot][pos / page_size], row pos % page_size of that page.
 // With `splits` > 0 the projection row is read as the sum of that many float
 // partial rows (the K-split partial sums of the projection, in split order)
 // instead of from qkv; the rotated queries are still written to qkv.
@@ -99,47 +98,65 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
                                         const int* __restrict__ page_table, int max_pages, int page_size,
                                         int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
                                         int interleaved, int write_kv) {
+    // One block per token.  The angle of a pair depends on the position only, so its sine and
+    // cosine are computed once and shared by every head of the row.
+    extern __shared__ float sc[];                  // [rotary_dim/2] sines, then cosines
     chain_release();
     chain_wait();
     const int t = blockIdx.x;
-    const int h = blockIdx.y;
     const int pos = tok_pos[t];
-    T* src = qkv + (size_t)t * row_stride + (size_t)h * head_dim;
-    T* dst = src;
-    const float* psrc = partial + (size_t)t * partial_width + (size_t)h * head_dim;
-    auto load = [&](int d) -> float {
-        if (splits == 0) return to_float(src[d]);
+    const int half = rotary_dim / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        sc[i] = s; sc[half + i] = c;
+    }
+    __syncthreads();
+    T* row = qkv + (size_t)t * row_stride;
+    const float* prow = partial + (size_t)t * partial_width;
+    auto load = [&](int col) -> float {
+        if (splits == 0) return to_float(row[col]);
         float a = 0.f;
-        for (int sidx = 0; sidx < splits; ++sidx) a += psrc[(size_t)sidx * split_stride + d];
+        for (int sidx = 0; sidx < splits; ++sidx) a += prow[(size_t)sidx * split_stride + col];
         return a;
     };
-    bool rotate = true;
-    if (h >= n_heads) {
-        if (!write_kv) return;
-        const int kvh = (h - n_heads) % n_kv_heads;
-        const bool is_v = (h - n_heads) >= n_kv_heads;
+    size_t cache_row = 0;
+    if (write_kv) {
         const int slot = seq_slot[tok_seq[t]];
-        T* cache = is_v ? v_cache : k_cache;
         const int page = page_table[(size_t)slot * max_pages + pos / page_size];
-        dst = cache + (((size_t)page * page_size + (size_t)(pos % page_size)) * n_kv_heads + kvh) * head_dim;
-        rotate = !is_v;
+        cache_row = ((size_t)page * page_size + (size_t)(pos % page_size)) * n_kv_heads;
     }
-    const int half = rotary_dim / 2;
-    if (rotate) {
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const int d0 = interleaved ? 2 * i : i;
-            const int d1 = interleaved ? 2 * i + 1 : i + half;
-            const float a = (float)pos * inv_freq[i];
-            float s, c;
-            sincosf(a, &s, &c);
-            const float x0 = load(d0), x1 = load(d1);
-            dst[d0] = from_float<T>(x0 * c - x1 * s);
-            dst[d1] = from_float<T>(x0 * s + x1 * c);
+    // blockIdx.y divides the heads of the row [q | k | v] among blocks (few tokens: many blocks per token)
+    const int total_heads = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    const int per_block = (total_heads + gridDim.y - 1) / gridDim.y;
+    const int h_lo = blockIdx.y * per_block, h_hi = min(total_heads, h_lo + per_block);
+    const int rot_end = min(h_hi, n_heads + (write_kv ? n_kv_heads : 0));      // q and k rotate, v does not
+    // rotated pairs
+    for (int i = threadIdx.x; i < (rot_end - h_lo) * half; i += blockDim.x) {
+        const int h = h_lo + i / half, pr = i % half;
+        const int d0 = interleaved ? 2 * pr : pr, d1 = interleaved ? 2 * pr + 1 : pr + half;
+        const float x0 = load(h * head_dim + d0), x1 = load(h * head_dim + d1);
+        const float s = sc[pr], c = sc[half + pr];
+        T* dst = h < n_heads ? row + (size_t)h * head_dim
+                             : k_cache + (cache_row + (h - n_heads)) * head_dim;
+        dst[d0] = from_float<T>(x0 * c - x1 * s);
+        dst[d1] = from_float<T>(x0 * s + x1 * c);
+    }
+    // what is not rotated: the tail of q and k beyond rotary_dim, and v
+    const int tail = head_dim - rotary_dim;
+    if (tail > 0) {
+        for (int i = threadIdx.x; i < (rot_end - h_lo) * tail; i += blockDim.x) {
+            const int h = h_lo + i / tail, d = rotary_dim + i % tail;
+            if (h < n_heads) { if (splits > 0) row[(size_t)h * head_dim + d] = from_float<T>(load(h * head_dim + d)); }
+            else k_cache[(cache_row + (h - n_heads)) * head_dim + d] = from_float<T>(load(h * head_dim + d));
         }
-        if (dst != src || splits > 0)
-            for (int d = rotary_dim + threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = from_float<T>(load(d));
-    } else {
-        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = from_float<T>(load(d));
+    }
+    const int v_lo = max(h_lo, n_heads + n_kv_heads);
+    if (write_kv && h_hi > v_lo) {
+        for (int i = threadIdx.x; i < (h_hi - v_lo) * head_dim; i += blockDim.x) {
+            const int col = v_lo * head_dim + i;                       // column in the projection row
+            v_cache[cache_row * head_dim + (col - (n_heads + n_kv_heads) * head_dim)] = from_float<T>(load(col));
+        }
     }
 }
 
@@ -169,7 +186,10 @@ template <typename TO, typename TW>
 static void launch_rmsnorm(float* x, const float* partial, int splits, size_t split_stride, const TW* w,
                            const int* rows, TO* y, int n_rows, int width, float eps, cudaStream_t stream) {
     auto threads_for = [&](int per) { int t = ((width + per - 1) / per + 31) / 32 * 32; return t < 64 ? 64 : t; };
-    if (width <= 4096)
+    if (n_rows >= 512 && width <= 16384 && width > 1024)
+        // many rows: a quarter of the threads per row, four times the rows in flight per SM
+        launch_chained(rmsnorm_kernel<TO, TW, 16>, dim3(n_rows), dim3(threads_for(16)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
+    else if (width <= 4096)
         launch_chained(rmsnorm_kernel<TO, TW, 4>, dim3(n_rows), dim3(threads_for(4)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
     else if (width <= 8192)
         launch_chained(rmsnorm_kernel<TO, TW, 8>, dim3(n_rows), dim3(threads_for(8)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
@@ -230,12 +250,16 @@ int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const float* par
     MDMA_REQUIRE(!write_kv || (page_table && page_size > 0 && max_pages > 0), "rope_cache_write: no cache pages");
     MDMA_REQUIRE(splits >= 0 && (splits == 0 || partial), "rope_cache_write: partial sums need a pointer");
     if (n_tokens == 0) return 0;
-    const int heads = n_heads + (write_kv ? 2 * n_kv_heads : 0);
-    dim3 grid(n_tokens, heads);
-    int threads = 32;
-    while (threads < head_dim / 2 && threads < 128) threads *= 2;
+    // about 300 blocks at least: few tokens get several blocks per row, many tokens one
+    const int total_heads = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    int per_token = n_tokens >= 300 ? 1 : (n_tokens <= 128 ? total_heads : (300 + n_tokens - 1) / n_tokens);
+    if (per_token > total_heads) per_token = total_heads;
+    dim3 grid(n_tokens, per_token);
+    const int work = ((total_heads + per_token - 1) / per_token) * head_dim / 2;
+    const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+    const size_t smem = (size_t)rotary_dim * sizeof(float);
     MDMA_DISPATCH_DTYPE(dtype, T,
-        launch_chained(rope_cache_write_kernel<T>, grid, dim3(threads), 0, stream,
+        launch_chained(rope_cache_write_kernel<T>, grid, dim3(threads), smem, stream,
             (T*)qkv, row_stride, partial, splits, (size_t)split_stride, partial_width,
             tok_seq, tok_pos, seq_slot, inv_freq, (T*)k_cache, (T*)v_cache,
             page_table, max_pages, page_size, n_heads, n_kv_heads, head_dim, rotary_dim, interleaved, write_kv));
