@@ -34,7 +34,8 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
 // PER > 0: each thread keeps PER elements of the row in registers (one read of
 // x); PER == 0: rows of any width, read twice.
 template <typename TO, typename TW, int PER>
-__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ partial, int splits,
+__global__ void __launch_bounds__(1024)
+rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ partial, int splits,
                                size_t split_stride, const TW* __restrict__ w, const int* __restrict__ rows,
                                TO* __restrict__ y, int width, float eps) {
     chain_release();
@@ -46,19 +47,31 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     TO* yr = y + (size_t)r * width;
     float ss = 0.f;
     if (PER > 0) {
+        // All loads of the row are issued before anything is written back to x: a store in
+        // between would order the loads behind it (same array) and serialise PER round trips.
         float v[PER > 0 ? PER : 1];
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int e = i * blockDim.x + threadIdx.x;
-            float a = 0.f;
-            if (e < width) {
-                a = xr[e];
-                for (int sidx = 0; sidx < splits; ++sidx) a += partial[(size_t)sidx * split_stride + src + e];
-                if (splits > 0) xr[e] = a;
-            }
-            v[i] = a;
-            ss += a * a;
+            v[i] = e < width ? xr[e] : 0.f;
         }
+        if (splits > 0) {
+            for (int sidx = 0; sidx < splits; ++sidx) {
+                const float* pr = partial + (size_t)sidx * split_stride + src;
+#pragma unroll
+                for (int i = 0; i < PER; ++i) {
+                    const int e = i * blockDim.x + threadIdx.x;
+                    if (e < width) v[i] += pr[e];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int e = i * blockDim.x + threadIdx.x;
+                if (e < width) xr[e] = v[i];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) ss += v[i] * v[i];
         ss = block_sum(ss, scratch);
         const float scale = 1.0f / sqrtf(ss / (float)width + eps);
 #pragma unroll
@@ -77,6 +90,72 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
         const float scale = 1.0f / sqrtf(ss / (float)width + eps);
         for (int e = threadIdx.x; e < width; e += blockDim.x)
             yr[e] = from_float<TO>(xr[e] * scale * to_float(w[e]));
+    }
+}
+
+// The same for widths that are a multiple of 4: each thread keeps NV groups of four
+// consecutive elements (16-byte loads of x and of the partial sums).
+template <typename T> struct Pack4;
+template <> struct Pack4<float> {
+    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    }
+};
+template <> struct Pack4<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+template <typename TO, typename TW, int NV>
+__global__ void __launch_bounds__(1024)
+rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int splits, size_t split_stride,
+                   const TW* __restrict__ w, const int* __restrict__ rows, TO* __restrict__ y, int width, float eps) {
+    __shared__ float scratch[32];
+    chain_release();
+    chain_wait();
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * width;
+    float4* xr = reinterpret_cast<float4*>(x + src);
+    const int n4 = width / 4;
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int e = i * blockDim.x + threadIdx.x;
+        v[i] = e < n4 ? xr[e] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (splits > 0) {
+        for (int sidx = 0; sidx < splits; ++sidx) {
+            const float4* pr = reinterpret_cast<const float4*>(partial + (size_t)sidx * split_stride + src);
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int e = i * blockDim.x + threadIdx.x;
+                if (e < n4) { const float4 q = pr[e]; v[i].x += q.x; v[i].y += q.y; v[i].z += q.z; v[i].w += q.w; }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < n4) xr[e] = v[i];
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TO* yr = y + (size_t)r * width;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int e = i * blockDim.x + threadIdx.x;
+        if (e < n4) {
+            const TW* wp = w + 4 * e;
+            Pack4<TO>::store(yr + 4 * e, v[i].x * scale * to_float(wp[0]), v[i].y * scale * to_float(wp[1]),
+                             v[i].z * scale * to_float(wp[2]), v[i].w * scale * to_float(wp[3]));
+        }
     }
 }
 
@@ -186,6 +265,18 @@ template <typename TO, typename TW>
 static void launch_rmsnorm(float* x, const float* partial, int splits, size_t split_stride, const TW* w,
                            const int* rows, TO* y, int n_rows, int width, float eps, cudaStream_t stream) {
     auto threads_for = [&](int per) { int t = ((width + per - 1) / per + 31) / 32 * 32; return t < 64 ? 64 : t; };
+    const bool aligned = width % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)partial & 15) == 0 &&
+                         ((uintptr_t)y & 15) == 0 && split_stride % 4 == 0;
+    if (aligned && width <= 16384) {
+        // 16-byte accesses; many rows: few threads per row (more rows in flight), few rows: many threads
+        if (n_rows >= 512 && width > 1024)
+            launch_chained(rmsnorm_vec_kernel<TO, TW, 4>, dim3(n_rows), dim3(threads_for(16)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
+        else if (width <= 4096)
+            launch_chained(rmsnorm_vec_kernel<TO, TW, 1>, dim3(n_rows), dim3(threads_for(4)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
+        else
+            launch_chained(rmsnorm_vec_kernel<TO, TW, 4>, dim3(n_rows), dim3(threads_for(16)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
+        return;
+    }
     if (n_rows >= 512 && width <= 16384 && width > 1024)
         // many rows: a quarter of the threads per row, four times the rows in flight per SM
         launch_chained(rmsnorm_kernel<TO, TW, 16>, dim3(n_rows), dim3(threads_for(16)), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
