@@ -228,9 +228,13 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"the sequence in slot {e.slot} brings no tokens")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise StepError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+            toks = np.asarray(e.tokens)
+            if toks.dtype.kind not in "iu" or toks.ndim != 1:
+                raise StepError(f"token ids of slot {e.slot} must be a flat list of integers")
+            lo, hi = int(toks.min()), int(toks.max())
+            if lo < 0 or hi >= self.vocab_size:
+                bad = lo if lo < 0 else hi
+                raise StepError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"wanted place {w} is outside the {n} tokens of slot {e.slot}")
@@ -279,22 +283,30 @@ class Engine:
         ids, tok_seq, tok_pos, seq_slot, seq_start, seq_pos0 = [], [], [], [], [0], []
         want_rows, dest_rows = [], []
         max_new = max_len = 0
+        n_rows = 0
         for s, (i, start, take) in enumerate(pieces):
             e = entries[i]
             pos0 = base[i] + start
             seq_slot.append(e.slot)
             seq_pos0.append(pos0)
-            first_row = len(ids)
-            ids.extend(int(t) for t in e.tokens[start:start + take])
-            tok_seq.extend([s] * take)
-            tok_pos.extend(range(pos0, pos0 + take))
-            seq_start.append(len(ids))
+            first_row = n_rows
+            ids.append(np.asarray(e.tokens[start:start + take], dtype=np.int32))
+            tok_seq.append(np.full(take, s, dtype=np.int32))
+            tok_pos.append(np.arange(pos0, pos0 + take, dtype=np.int32))
+            n_rows += take
+            seq_start.append(n_rows)
             max_new = max(max_new, take)
             max_len = max(max_len, pos0 + take)
-            for j in range(start, start + take):
-                for dest in out_row.get((i, j), ()):
-                    want_rows.append(first_row + j - start)
-                    dest_rows.append(dest)
+            for j in sorted({int(w) for w in e.want}):
+                if start <= j < start + take:
+                    for dest in out_row.get((i, j), ()):
+                        want_rows.append(first_row + j - start)
+                        dest_rows.append(dest)
+        if want_rows:          # keep the result rows in the order of the entries and of each `want`
+            order = sorted(range(len(dest_rows)), key=dest_rows.__getitem__)
+            want_rows = [want_rows[k] for k in order]
+            dest_rows = [dest_rows[k] for k in order]
+        ids, tok_seq, tok_pos = np.concatenate(ids), np.concatenate(tok_seq), np.concatenate(tok_pos)
         T, B, W = len(ids), len(pieces), len(want_rows)
         fields = [ids, tok_seq, tok_pos, seq_slot, seq_start, seq_pos0, want_rows]
         flat = np.concatenate([np.asarray(f, dtype=np.int32) for f in fields]) if T else None
