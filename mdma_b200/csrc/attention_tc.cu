@@ -8,12 +8,14 @@
 //                      accumulator in tensor memory (two S buffers)
 //     softmax          128 threads, one query row each: tcgen05.ld of the row, mask, running maximum and
 //                      sum in float, P rounded to bfloat16 and written to shared memory in the operand layout
-//     O_blk = P V      tcgen05.mma, M=128, N=head_dim, V taken MN-major straight from the cache tile
-//     O += O_blk       each thread folds its row of O_blk (tensor memory, two buffers) into registers,
-//                      rescaled by the change of its maximum
+//     O += P V         tcgen05.mma accumulating in tensor memory, M=128, N=head_dim, V taken MN-major
+//                      straight from the cache tile
+// The probabilities are taken against a reference maximum that is only moved when the row's true
+// maximum has grown by more than 2^8 since; only then is the accumulator in tensor memory rescaled
+// (read, multiplied, written back), which happens in the first blocks of a row and hardly after.
 // Roles: warp 0 issues TMA loads (Q once, K/V through a ring), warp 1 issues the MMAs (S of block b+1 is
 // issued before P V of block b, so the tensor pipe works under the softmax), warps 2-5 are the softmax
-// rows.  Every wait is bounded.
+// rows.  Two blocks fit an SM, so one block's softmax runs under the other's MMAs.  Every wait is bounded.
 // Limits: head_dim a multiple of 16 up to 128, group size up to 128, page size a multiple of 64.
 #include <mutex>
 #include <unordered_map>
@@ -23,7 +25,7 @@
 
 namespace mdma {
 
-constexpr int kTcRows = 128, kTcKeys = 64, kTcThreadsA = 192, kKvStages = 3;
+constexpr int kTcRows = 128, kTcKeys = 64, kTcThreadsA = 192, kKvStages = 2;
 
 struct AttnTcParams {
     const int* seq_start; const int* seq_pos0; const int* seq_slot;
@@ -38,51 +40,54 @@ struct AttnTcParams {
 //   Q: 2 halves x [128 rows x 128 B]           32 KB
 //   K ring: stages x 2 halves x [64 x 128 B]   stages x 16 KB
 //   V ring: same
-//   P: 2 buffers x [128 rows x 128 B]          32 KB
+//   P: [128 rows x 128 B]                      16 KB
 constexpr int kQHalf = kTcRows * 128, kKvHalf = kTcKeys * 128, kPBuf = kTcRows * 128;
 constexpr int kSmemQ = 0, kSmemK = 2 * kQHalf, kSmemV = kSmemK + kKvStages * 2 * kKvHalf,
-              kSmemP = kSmemV + kKvStages * 2 * kKvHalf, kSmemBars = kSmemP + 2 * kPBuf,
-              kAttnTcSmem = kSmemBars + 256 + 1024;
+              kSmemP = kSmemV + kKvStages * 2 * kKvHalf, kSmemBars = kSmemP + kPBuf,
+              kAttnTcSmem = kSmemBars + 256;       // 112.25 KB: two blocks per SM
 
-__global__ void __launch_bounds__(kTcThreadsA)
+__global__ void __launch_bounds__(kTcThreadsA, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
-    uint8_t* base_ptr = smem_raw + (base - ptx::smem_addr(smem_raw));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t base = ptx::smem_addr(smem_raw);
+    uint8_t* base_ptr = smem_raw;
     const uint32_t bars = base + kSmemBars;
-    // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], p_ready[2], o_full[2]
+    // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], p_ready, pv_done
     const uint32_t q_full = bars;
     auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
     auto kv_empty = [&](int s) { return bars + 8u * (1 + kKvStages + s); };
     auto s_full = [&](int i) { return bars + 8u * (1 + 2 * kKvStages + i); };
-    auto p_ready = [&](int i) { return bars + 8u * (3 + 2 * kKvStages + i); };
-    auto o_full = [&](int i) { return bars + 8u * (5 + 2 * kKvStages + i); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + kSmemBars + 8 * (7 + 2 * kKvStages));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kSmemBars + 8 * (8 + 2 * kKvStages));
+    const uint32_t p_ready = bars + 8u * (3 + 2 * kKvStages), pv_done = bars + 8u * (4 + 2 * kKvStages);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + kSmemBars + 8 * (5 + 2 * kKvStages));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kSmemBars + 8 * (6 + 2 * kKvStages));
 
     chain_release();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = blockIdx.y, kvh = blockIdx.z;
     if (threadIdx.x == 0) {
+        if (base & 1023u) *abort_flag = 1;          // the tiles need 1024-byte alignment (checked again below)
         ptx::mbar_init(q_full, 1);
         for (int s = 0; s < kKvStages; ++s) { ptx::mbar_init(kv_full(s), 1); ptx::mbar_init(kv_empty(s), 1); }
-        for (int i = 0; i < 2; ++i) { ptx::mbar_init(s_full(i), 1); ptx::mbar_init(p_ready(i), 128); ptx::mbar_init(o_full(i), 1); }
-        *abort_flag = 0;
+        for (int i = 0; i < 2; ++i) ptx::mbar_init(s_full(i), 1);
+        ptx::mbar_init(p_ready, 128);
+        ptx::mbar_init(pv_done, 1);
+        if (!(base & 1023u)) *abort_flag = 0;
         ptx::fence_mbar_init();
     }
-    if (warp == 1) { ptx::tmem_alloc(ptx::smem_addr((const void*)tmem_slot), 512); ptx::tmem_relinquish(); }
+    if (warp == 1) { ptx::tmem_alloc(ptx::smem_addr((const void*)tmem_slot), 256); ptx::tmem_relinquish(); }
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;     // S: 2 x 64 columns, O: 2 x 128 columns
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;     // S: 2 x 64 columns, O: 128 columns
 
     chain_wait();
     const int row0_seq = p.seq_start[seq];
     const int n_new = p.seq_start[seq + 1] - row0_seq;
-    const int tok0 = blockIdx.x * p.tile_tokens;
-    const bool active = tok0 < n_new;                 // uniform over the block
+    // late tiles see the most keys: they are handed out first so that the short ones fill the tail
+    const int tok0 = (int)(gridDim.x - 1 - blockIdx.x) * p.tile_tokens;
+    const bool active = tok0 < n_new && !(base & 1023u);      // uniform over the block
     const int n_tok = active ? min(p.tile_tokens, n_new - tok0) : 0;
     const int pos0 = p.seq_pos0[seq] + tok0;
     const int last_pos = pos0 + n_tok - 1;
@@ -132,17 +137,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 ptx::tc_fence_after_sync();
                 issue_s(i + 1);
             }
-            ok = ptx::mbar_wait(p_ready(i & 1), (i >> 1) & 1, abort_flag);
+            ok = ptx::mbar_wait(p_ready, i & 1, abort_flag);
             if (!ok) break;
             ptx::tc_fence_after_sync();
             const int s = i % kKvStages;
-            for (int kk = 0; kk < kTcKeys / 16; ++kk) {     // O[i%2] = P(i) V(i): K dimension = keys
-                const uint32_t pa = base + kSmemP + (i & 1) * kPBuf + kk * 32;
+            for (int kk = 0; kk < kTcKeys / 16; ++kk) {     // O += P(i) V(i): K dimension = keys
+                const uint32_t pa = base + kSmemP + kk * 32;
                 const uint32_t vb = base + kSmemV + (s * 2) * kKvHalf + kk * 16 * 128;
-                ptx::mma_bf16_ss(tmem_o + (i & 1) * 128, ptx::smem_desc_sw128(pa),
-                                 ptx::smem_desc_sw128_mn(vb, kKvHalf), idesc_o, kk > 0);
+                ptx::mma_bf16_ss(tmem_o, ptx::smem_desc_sw128(pa), ptx::smem_desc_sw128_mn(vb, kKvHalf), idesc_o,
+                                 (i > 0 || kk > 0) ? 1u : 0u);
             }
-            ptx::mma_commit(o_full(i & 1));
+            ptx::mma_commit(pv_done);
             ptx::mma_commit(kv_empty(s));
         }
     } else if (active && warp >= 2) {
@@ -154,91 +159,112 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const bool row_valid = t < n_tok;
         const int pos = pos0 + (row_valid ? t : n_tok - 1);
         const int win = p.window > 0 ? pos + 1 - p.window : 0;
-        float o[128];
-#pragma unroll
-        for (int d = 0; d < 128; ++d) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
-        uint8_t* p_rows = base_ptr + kSmemP + (size_t)r * 128;
+        float m_ref = -INFINITY, l = 0.f;                     // reference maximum (log2 domain), running sum
+        uint8_t* p_row = base_ptr + kSmemP + (size_t)r * 128;
         bool ok = true;
-        auto fold = [&](int i, float corr) {                 // o = o * corr + O_blk(i)
-            ok = ptx::mbar_wait(o_full(i & 1), (i >> 1) & 1, abort_flag);
-            if (!ok) return;
-            ptx::tc_fence_after_sync();
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                if (c * 32 < D) {
-                    float v[32];
-                    ptx::tmem_load_32_nowait(tmem_o + (i & 1) * 128 + lane_base + c * 32, v);
-                    ptx::tmem_load_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * corr + v[j];
-                }
-            }
-            ptx::tc_fence_before_sync();
-        };
         for (int i = 0; i < nb && ok; ++i) {
-            ok = ptx::mbar_wait(s_full(i & 1), (i >> 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ptx::mbar_wait(s_full(i & 1), (i >> 1) & 1, abort_flag));   // whole warps go on or stop
             if (!ok) break;
             ptx::tc_fence_after_sync();
             float sv[64];
             ptx::tmem_load_32_nowait(tmem_s + (i & 1) * 64 + lane_base, sv);
             ptx::tmem_load_32_nowait(tmem_s + (i & 1) * 64 + lane_base + 32, sv + 32);
             ptx::tmem_load_wait();
+            ptx::tc_fence_before_sync();
             const int key0 = (b0 + i) * kTcKeys;
             const bool need_mask = key0 + kTcKeys - 1 > pos || key0 < win;
-            float mx = m;
+            float mx = -INFINITY;
+            if (need_mask) {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-                float v = sv[j] * p.scale_log2;
-                if (need_mask && (key0 + j > pos || key0 + j < win)) v = -INFINITY;
-                sv[j] = v;
-                mx = fmaxf(mx, v);
-            }
-            const float ref = mx == -INFINITY ? 0.f : mx;
-            const float corr = exp2f(m - ref);
-            m = mx;
-            float sum = 0.f;
-            // P row: 64 bf16 = 8 chunks of 16 bytes, chunk c at position c ^ (row & 7)
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float p0 = exp2f(sv[c * 8 + 2 * j] - ref), p1 = exp2f(sv[c * 8 + 2 * j + 1] - ref);
-                    sum += p0 + p1;
-                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                    w[j] = *reinterpret_cast<uint32_t*>(&pk);
+                for (int j = 0; j < 64; ++j) {
+                    if (key0 + j > pos || key0 + j < win) sv[j] = -INFINITY;
+                    mx = fmaxf(mx, sv[j]);
                 }
-                *reinterpret_cast<uint4*>(p_rows + (size_t)(i & 1) * kPBuf + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) mx = fmaxf(mx, sv[j]);
+            }
+            mx *= p.scale_log2;                               // scale > 0: the maximum commutes with it
+            // move the reference only when the maximum has grown by more than 2^8 (or at the first keys)
+            float corr = 1.f;
+            bool moved = false;
+            if (mx > m_ref + 8.f) {
+                corr = m_ref == -INFINITY ? 0.f : ptx::ex2_approx(m_ref - mx);
+                m_ref = mx;
+                moved = true;
+            }
+            const float ref = m_ref == -INFINITY ? 0.f : m_ref;
+            float sum = 0.f;
+            uint32_t pk[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float p0 = ptx::ex2_approx(fmaf(sv[2 * j], p.scale_log2, -ref));
+                const float p1 = ptx::ex2_approx(fmaf(sv[2 * j + 1], p.scale_log2, -ref));
+                sum += p0 + p1;
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+                pk[j] = *reinterpret_cast<uint32_t*>(&b2);
             }
             l = l * corr + sum;
-            ptx::fence_proxy_async_shared();
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(p_ready(i & 1));
-            if (i > 0) fold(i - 1, corr_prev);
-            corr_prev = corr;
-        }
-        if (ok && nb > 0) fold(nb - 1, corr_prev);
-        if (ok && row_valid && nb > 0) {
-            const float inv = 1.0f / l;
-            __nv_bfloat16* dst = p.out + ((size_t)(row0_seq + tok0 + t) * p.n_heads + kvh * G + g) * D;
+            // P(i-1) V(i-1) must be done before P is overwritten and before O is rescaled
+            if (i > 0) {
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait(pv_done, (i - 1) & 1, abort_flag));
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, moved)) {          // rare: rescale this warp's rows of O
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                if (c * 8 < D) {
-                    uint32_t w[4];
+                    for (int c = 0; c < 4; ++c) {
+                        if (c * 32 < D) {
+                            float v[32];
+                            ptx::tmem_load_32_nowait(tmem_o + lane_base + c * 32, v);
+                            ptx::tmem_load_wait();
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        __nv_bfloat162 pk = __floats2bfloat162_rn(o[c * 8 + 2 * j] * inv, o[c * 8 + 2 * j + 1] * inv);
-                        w[j] = *reinterpret_cast<uint32_t*>(&pk);
+                            for (int j = 0; j < 32; ++j) v[j] *= corr;
+                            ptx::tmem_store_32_nowait(tmem_o + lane_base + c * 32, v);
+                        }
                     }
-                    *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    ptx::tmem_store_wait();
                 }
             }
+#pragma unroll
+            for (int c = 0; c < 8; ++c)      // 64 bf16 = 8 chunks of 16 bytes, chunk c at position c ^ (row & 7)
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            ptx::fence_proxy_async_shared();
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(p_ready);
+        }
+        if (ok && nb > 0) ok = __all_sync(0xffffffffu, ptx::mbar_wait(pv_done, (nb - 1) & 1, abort_flag));
+        if (ok && nb > 0) {
+            ptx::tc_fence_after_sync();
+            const float inv = 1.0f / l;
+            __nv_bfloat16* dst = p.out + ((size_t)(row0_seq + tok0 + (row_valid ? t : 0)) * p.n_heads + kvh * G + g) * D;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (c * 32 < D) {
+                    float v[32];
+                    ptx::tmem_load_32_nowait(tmem_o + lane_base + c * 32, v);
+                    ptx::tmem_load_wait();
+                    if (row_valid) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            if (c * 32 + q * 8 < D) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(v[q * 8 + 2 * j] * inv, v[q * 8 + 2 * j + 1] * inv);
+                                    w[j] = *reinterpret_cast<uint32_t*>(&b2);
+                                }
+                                *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
         }
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) { ptx::tc_fence_after_sync(); ptx::tmem_dealloc(tmem_base, 512); }
+    if (warp == 1) { ptx::tc_fence_after_sync(); ptx::tmem_dealloc(tmem_base, 256); }
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 2);
 }
 
@@ -298,6 +324,7 @@ int mdma_attention_tc(const void* q, int q_stride, int q_rows_cap, const void* k
     MDMA_REQUIRE(mdma_attention_tc_supported(n_heads, n_kv_heads, head_dim, page_size),
                  "attention_tc: heads %d / kv heads %d / head_dim %d / page %d is outside its limits", n_heads, n_kv_heads, head_dim, page_size);
     MDMA_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0, "attention_tc: query rows must be 16-byte aligned");
+    MDMA_REQUIRE(scale > 0.f, "attention_tc: the score scale must be positive");
     MDMA_REQUIRE(n_seqs <= 65535 && n_kv_heads <= 65535, "attention_tc: grid too large");
     if (n_tokens == 0 || n_seqs == 0) return 0;
     const int G = n_heads / n_kv_heads;
