@@ -14,7 +14,10 @@
 // result does not depend on timing.
 // Limits: head_dim a multiple of 16 up to 128; group size up to 64.
 #pragma once
+#include <mutex>
+
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace mdma {
 
@@ -58,6 +61,7 @@ struct AttnParams {
     float* part_o; float* part_ml;                  // split partials: [tokens, heads, splits, head_dim], [.., 2]
     int n_heads, n_kv_heads, head_dim, group, tile_tokens, window, splits;
     float scale_log2;                               // scale * log2(e)
+    int* status;                                    // optional device word, set non-zero if a wait ran out
 };
 
 // Tile shared-memory rows are DMAX elements wide; 16-byte chunk c of row r sits at chunk c ^ (r & 7).
@@ -71,7 +75,7 @@ __global__ void __launch_bounds__(kAttnThreads)
 attention_mma_kernel(const AttnParams p) {
     constexpr int kChunks = DMAX / 8;              // 16-byte chunks per row
     constexpr int kTile = kRows * DMAX * 2;        // bytes of one 64-row tile
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t sK = sQ + kTile, sV = sK + 2 * kTile;
 
@@ -267,7 +271,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3)
 attention_decode_kernel(const AttnParams p) {
     constexpr int kChunks = DMAX / 8;
     constexpr int kTile = KB * DMAX * 2;             // one 64-key K or V tile
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t s0 = (uint32_t)__cvta_generic_to_shared(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t sQ = s0;                              // 16 rows x DMAX
@@ -460,6 +464,206 @@ attention_decode_kernel(const AttnParams p) {
     }
 }
 
+// The same kernel with the key and value tiles fetched by TMA (one elected lane per warp issues a
+// tile load, completion on the warp's own mbarrier) instead of 16-byte cp.async copies, whose address
+// arithmetic was two thirds of the instructions.  Needs page_size to be a multiple of KB.  A tile is
+// stored as halves of 64 head elements: [KB keys x 128 bytes] with the 128-byte swizzle.
+template <int DMAX, int KB>
+__global__ void __launch_bounds__(kAttnThreads, 3)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const AttnParams p) {
+    constexpr int kChunks = DMAX / 8;
+    constexpr int kHalf = KB * 128;                      // one half tile: KB keys x 64 elements
+    constexpr int kTile = KB * DMAX * 2;                 // a K or V tile (DMAX/64 halves)
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t s0 = (uint32_t)__cvta_generic_to_shared(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sK = s0 + warp * 2 * kTile, sV = sK + kTile;      // tiles first: they need 1024-byte alignment
+    const uint32_t sQ = s0 + 4 * 2 * kTile;              // 16 rows x DMAX
+    const uint32_t bars = sQ + 16 * DMAX * 2;
+    const uint32_t kbar = bars + warp * 16, vbar = kbar + 8;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 4 * 2 * kTile + 16 * DMAX * 2 + 64);
+    auto kv_offset = [](int row, int chunk) -> uint32_t {      // 16-byte chunk of a key row inside a tile
+        return (uint32_t)((chunk >> 3) * kHalf + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+    };
+    if (threadIdx.x == 0) {
+        for (int w = 0; w < 4; ++w) { ptx::mbar_init(bars + w * 16, 1); ptx::mbar_init(bars + w * 16 + 8, 1); }
+        *abort_flag = (s0 & 1023u) ? 1 : 0;
+        ptx::fence_mbar_init();
+    }
+
+    chain_release();
+    chain_wait();
+    const int seq = blockIdx.y;
+    const int kvh = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+    const int token = p.seq_start[seq];
+    const int pos = p.seq_pos0[seq];
+    const int* pages = p.page_table + (size_t)p.seq_slot[seq] * p.max_pages;
+    const int D = p.head_dim, G = p.group, d_chunks = D / 8;
+    const int first_key = p.window > 0 ? max(0, pos + 1 - p.window) : 0;
+    const int blk_lo = first_key / KB, blk_hi = pos / KB + 1;
+    const int per = (blk_hi - blk_lo + p.splits - 1) / p.splits;
+    const int b0 = blk_lo + split * per, b1 = min(blk_hi, b0 + per);
+    const int halves = (D + 63) / 64;
+
+    auto load_tile = [&](const CUtensorMap* map, uint32_t dst, uint32_t bar, int blk) {      // one lane
+        const int key0 = blk * KB;
+        const int page = pages[key0 / p.page_size], row = key0 % p.page_size;
+        ptx::fence_proxy_async_shared();
+        ptx::mbar_expect_tx(bar, halves * kHalf);
+        for (int h = 0; h < halves; ++h) ptx::tma_load_4d(dst + h * kHalf, map, bar, h * 64, kvh, row, page);
+    };
+    int blk = b0 + warp;
+    if (*abort_flag != 0) blk = b1;
+    if (blk < b1 && lane == 0) { load_tile(&map_k, sK, kbar, blk); load_tile(&map_v, sV, vbar, blk); }
+    // Q rows (heads of the group) -> shared, zero beyond G and beyond D
+    for (int i = threadIdx.x; i < 16 * kChunks; i += kAttnThreads) {
+        const int r = i / kChunks, c = i % kChunks;
+        const bool valid = r < G && c < d_chunks;
+        const __nv_bfloat16* src = p.q + (size_t)token * p.q_stride + (size_t)(kvh * G + (valid ? r : 0)) * D + (valid ? c : 0) * 8;
+        cp_async_16(sQ + tile_offset<DMAX>(r, c), src, valid);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();                                     // Q is visible to all warps
+    uint32_t phase = 0;
+
+    uint32_t qf[DMAX / 16][4];
+#pragma unroll
+    for (int kd = 0; kd < DMAX / 16; ++kd)
+        ldmatrix_x4(sQ + tile_offset<DMAX>(lane & 15, kd * 2 + (lane >> 4)), qf[kd][0], qf[kd][1], qf[kd][2], qf[kd][3]);
+
+    const int win = p.window > 0 ? pos + 1 - p.window : 0;
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int n = 0; n < DMAX / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+    for (; blk < b1; blk += 4) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(kbar, phase, abort_flag))) break;     // this tile's K has landed
+        float s[KB / 8][4];
+#pragma unroll
+        for (int n = 0; n < KB / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+        for (int kd = 0; kd < DMAX / 16; ++kd) {
+            if (kd * 16 < D) {
+#pragma unroll
+                for (int n2 = 0; n2 < KB / 16; ++n2) {
+                    uint32_t k0, k1, k2, k3;
+                    const int krow = n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    ldmatrix_x4(sK + kv_offset(krow, kd * 2 + ((lane >> 3) & 1)), k0, k1, k2, k3);
+                    mma_16816(s[n2 * 2], qf[kd][0], qf[kd][1], qf[kd][2], qf[kd][3], k0, k1);
+                    mma_16816(s[n2 * 2 + 1], qf[kd][0], qf[kd][1], qf[kd][2], qf[kd][3], k2, k3);
+                }
+            }
+        }
+        __syncwarp();
+        const bool more = blk + 4 < b1;
+        if (more && lane == 0) load_tile(&map_k, sK, kbar, blk + 4);     // K buffer is free: fetch the next tile's keys
+        const int key_base = blk * KB + (lane & 3) * 2;
+        float mx_lo = m_lo, mx_hi = m_hi;
+#pragma unroll
+        for (int n = 0; n < KB / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key_base + n * 8 + e;
+                const bool vis = key <= pos && key >= win;
+                const float v_lo = vis ? s[n][e] * p.scale_log2 : -INFINITY;
+                const float v_hi = vis ? s[n][2 + e] * p.scale_log2 : -INFINITY;
+                s[n][e] = v_lo; s[n][2 + e] = v_hi;
+                mx_lo = fmaxf(mx_lo, v_lo); mx_hi = fmaxf(mx_hi, v_hi);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float ref_lo = mx_lo == -INFINITY ? 0.f : mx_lo, ref_hi = mx_hi == -INFINITY ? 0.f : mx_hi;
+        const float corr_lo = exp2f(m_lo - ref_lo), corr_hi = exp2f(m_hi - ref_hi);
+        m_lo = mx_lo; m_hi = mx_hi;
+        float sum_lo = 0.f, sum_hi = 0.f;
+        uint32_t pa[KB / 16][4];
+#pragma unroll
+        for (int n = 0; n < KB / 8; ++n) {
+            const float p0 = exp2f(s[n][0] - ref_lo), p1 = exp2f(s[n][1] - ref_lo);
+            const float p2 = exp2f(s[n][2] - ref_hi), p3 = exp2f(s[n][3] - ref_hi);
+            sum_lo += p0 + p1; sum_hi += p2 + p3;
+            pa[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+            pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l_lo = l_lo * corr_lo + sum_lo; l_hi = l_hi * corr_hi + sum_hi;
+#pragma unroll
+        for (int n = 0; n < DMAX / 8; ++n) {
+            o[n][0] *= corr_lo; o[n][1] *= corr_lo; o[n][2] *= corr_hi; o[n][3] *= corr_hi;
+        }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(vbar, phase, abort_flag))) break;     // this tile's V has landed
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; ++kk) {
+#pragma unroll
+            for (int n2 = 0; n2 < DMAX / 16; ++n2) {
+                if (n2 * 16 < D) {
+                    uint32_t v0, v1, v2, v3;
+                    const int vrow = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                    ldmatrix_x4_trans(sV + kv_offset(vrow, n2 * 2 + (lane >> 4)), v0, v1, v2, v3);
+                    mma_16816(o[n2 * 2], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], v0, v1);
+                    mma_16816(o[n2 * 2 + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], v2, v3);
+                }
+            }
+        }
+        __syncwarp();
+        if (more && lane == 0) load_tile(&map_v, sV, vbar, blk + 4);
+        phase ^= 1u;
+    }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+    // ---- combine the four warps' states in warp order ---------------------------
+    // layout in shared memory (reusing the tiles): per warp [16 rows][DMAX + 2] floats
+    __syncthreads();
+    float* comb = reinterpret_cast<float*>(smem);
+    constexpr int kRowF = DMAX + 2;
+    {
+        float* mine = comb + (size_t)warp * 16 * kRowF;
+        const int r_lo = lane >> 2, r_hi = r_lo + 8;
+#pragma unroll
+        for (int n = 0; n < DMAX / 8; ++n) {
+            const int d = n * 8 + (lane & 3) * 2;
+            mine[r_lo * kRowF + d] = o[n][0]; mine[r_lo * kRowF + d + 1] = o[n][1];
+            mine[r_hi * kRowF + d] = o[n][2]; mine[r_hi * kRowF + d + 1] = o[n][3];
+        }
+        if ((lane & 3) == 0) {
+            mine[r_lo * kRowF + DMAX] = m_lo; mine[r_lo * kRowF + DMAX + 1] = l_lo;
+            mine[r_hi * kRowF + DMAX] = m_hi; mine[r_hi * kRowF + DMAX + 1] = l_hi;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * D; i += kAttnThreads) {
+        const int r = i / D, d = i % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, comb[((size_t)w * 16 + r) * kRowF + DMAX]);
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = comb[((size_t)w * 16 + r) * kRowF + DMAX];
+            if (mw != -INFINITY) {
+                const float f = exp2f(mw - m);
+                l += f * comb[((size_t)w * 16 + r) * kRowF + DMAX + 1];
+                acc += f * comb[((size_t)w * 16 + r) * kRowF + d];
+            }
+        }
+        const int head = kvh * G + r;
+        if (p.splits == 1) {
+            p.out[((size_t)token * p.n_heads + head) * D + d] = __float2bfloat16_rn(acc / l);
+        } else {
+            const size_t slot = ((size_t)token * p.n_heads + head) * p.splits + split;
+            p.part_o[slot * D + d] = acc;
+            if (d == 0) { p.part_ml[slot * 2] = m; p.part_ml[slot * 2 + 1] = l; }
+        }
+    }
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 4);
+}
+
 // out[token, head, :] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, splits taken in order.
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int splits, int head_dim) {
@@ -492,11 +696,42 @@ static inline long attention_mma_scratch_floats(int n_tokens, int n_heads, int h
     return splits > 1 ? (long)n_tokens * n_heads * splits * (head_dim + 2) : 0;
 }
 
+typedef CUresult (*AttnEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// A tensor map over a cache [pages, page_size, kv_heads, head_dim] with boxes of 64 elements x 1 head x
+// `box_keys` keys x 1 page (128-byte swizzle).
+static int make_cache_map(CUtensorMap* out, const void* cache, int n_pages, int page_size, int n_kv_heads,
+                          int head_dim, int box_keys) {
+    static AttnEncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<AttnEncodeTiledFn>(sym);
+    });
+    if (!fn) return fail("attention: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)n_kv_heads, (cuuint64_t)page_size, (cuuint64_t)n_pages};
+    cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, (cuuint64_t)n_kv_heads * head_dim * 2,
+                             (cuuint64_t)page_size * n_kv_heads * head_dim * 2};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_keys, 1};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("attention: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return 0;
+}
+
+// `n_pages` > 0 tells how many pages the caches hold and lets the decode kernel fetch tiles by TMA.
 static int launch_attention_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                        const int* seq_start, const int* seq_pos0, const int* seq_slot, const int* page_table,
                        int max_pages, int page_size, void* out, int n_tokens, int n_seqs, int max_new,
                        int n_heads, int n_kv_heads, int head_dim, int window, float scale, int splits,
-                       float* scratch, long scratch_floats, cudaStream_t stream) {
+                       float* scratch, long scratch_floats, cudaStream_t stream, int n_pages = 0,
+                       int* status = nullptr) {
     MDMA_REQUIRE(attention_mma_supported(n_heads, n_kv_heads, head_dim),
                  "attention_mma: heads %d / kv heads %d / head_dim %d is outside its limits (head_dim a multiple of 16 up to 128, group up to 64)",
                  n_heads, n_kv_heads, head_dim);
@@ -514,7 +749,7 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.group = n_heads / n_kv_heads; p.tile_tokens = kRows / p.group; p.window = window; p.splits = splits;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.part_o = nullptr; p.part_ml = nullptr;
+    p.part_o = nullptr; p.part_ml = nullptr; p.status = status;
     if (splits > 1) {
         const long need = attention_mma_scratch_floats(n_tokens, n_heads, head_dim, splits);
         MDMA_REQUIRE(scratch && scratch_floats >= need, "attention_mma: %d splits need %ld floats of scratch, %ld given", splits, need, scratch_floats);
@@ -522,7 +757,25 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
         p.part_ml = scratch + (long)n_tokens * n_heads * splits * head_dim;
     }
     dim3 grid((max_new + p.tile_tokens - 1) / p.tile_tokens, n_seqs, n_kv_heads * splits);
-    if (max_new == 1 && p.group <= 16) {
+    const bool tma_ok = n_pages > 0 && page_size % kDecodeKeys == 0 && ((uintptr_t)k_cache & 15) == 0 &&
+                        ((uintptr_t)v_cache & 15) == 0;
+    if (max_new == 1 && p.group <= 16 && tma_ok) {
+        // one token per sequence, tiles by TMA
+        CUtensorMap mk, mv;
+        if (int rc = make_cache_map(&mk, k_cache, n_pages, page_size, n_kv_heads, head_dim, kDecodeKeys)) return rc;
+        if (int rc = make_cache_map(&mv, v_cache, n_pages, page_size, n_kv_heads, head_dim, kDecodeKeys)) return rc;
+        if (head_dim <= 64) {
+            constexpr int bytes = 4 * 2 * kDecodeKeys * 64 * 2 + 16 * 64 * 2 + 128;
+            static bool once = false;
+            if (!once) { cudaFuncSetAttribute(attention_decode_tma_kernel<64, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
+            launch_chained(attention_decode_tma_kernel<64, kDecodeKeys>, grid, dim3(kAttnThreads), bytes, stream, mk, mv, p);
+        } else {
+            constexpr int bytes = 4 * 2 * kDecodeKeys * 128 * 2 + 16 * 128 * 2 + 128;
+            static bool once = false;
+            if (!once) { cudaFuncSetAttribute(attention_decode_tma_kernel<128, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
+            launch_chained(attention_decode_tma_kernel<128, kDecodeKeys>, grid, dim3(kAttnThreads), bytes, stream, mk, mv, p);
+        }
+    } else if (max_new == 1 && p.group <= 16) {
         // one token per sequence: the decode kernel (no padding rows beyond one 16-row tile)
         if (head_dim <= 64) {
             constexpr int bytes = 16 * 64 * 2 + 4 * 2 * kDecodeKeys * 64 * 2;

@@ -193,9 +193,9 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("attention scratch is too small and cannot grow during graph capture")
         reserve_scratch(qkv.device, need)
-    _call("tensor", "mdma_attention_mma", _ptr(qkv), _i(qkv.stride(0)), _ptr(view.k), _ptr(view.v),
-          _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
+    _call("tensor", "mdma_attention_mma_paged", _ptr(qkv), _i(qkv.stride(0)), _ptr(view.k), _ptr(view.v),
+          _i(view.k.shape[0] if view.k.is_contiguous() and view.v.is_contiguous() else 0), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
           _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs),
           _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale), _i(splits),
-          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _stream(),
+          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]), _stream(),
           launches=2 if splits > 1 else 1)
