@@ -162,8 +162,8 @@ __device__ Crossing find_crossing(const float* __restrict__ probs, int vocab, un
     // the kth tied element by index: block-wide ordered count over chunks
     int* counter = misc + 1;     // running count of ties before the current chunk
     int* answer = misc + 2;
-    int* total_ties = misc + 3;
-    if (threadIdx.x == 0) { *counter = 0; *answer = -1; *total_ties = 0; }
+    int* last_index = misc + 3;      // the highest index among the ties
+    if (threadIdx.x == 0) { *counter = 0; *answer = -1; *last_index = 0; }
     __syncthreads();
     __shared__ int warp_counts[32];
     int last_tie = -1;
@@ -188,18 +188,19 @@ __device__ Crossing find_crossing(const float* __restrict__ probs, int vocab, un
         __syncthreads();
         if (*answer >= 0) break;
     }
-    // fewer ties than asked for (rounding): take the last tied element
+    // fewer ties than asked for (fixed-point rounding of the masses): take the last tied element,
+    // and count only the ties that exist
     if (*answer < 0) {
-        atomicMax(total_ties, last_tie);
+        atomicMax(last_index, last_tie);
         __syncthreads();
-        if (threadIdx.x == 0) { *answer = *total_ties; kth = *counter; }
+        if (threadIdx.x == 0) *answer = *last_index;
         __syncthreads();
+        kth = *counter > 0 ? *counter : 1;
     }
     Crossing c;
     c.index = *answer;
     c.bits = prefix;
-    const int taken = min((long long)*counter > 0 ? (long long)*counter : kth, kth);
-    c.mass = above + unit * (unsigned long long)(taken > 0 ? taken : 1);
+    c.mass = above + unit * (unsigned long long)kth;
     __syncthreads();
     return c;
 }
