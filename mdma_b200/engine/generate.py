@@ -108,6 +108,7 @@ class Generator:
         live = [_Live(r, self.engine.acquire(), budgets[r][0], budgets[r][1]) for r in batch]
         penalised = params.repetition_penalty != 1.0 and params.repetition_window > 0
         session = None
+        session_fresh = False          # whether the session's device buffers describe this batch
         try:
             entries = [StepEntry(s.slot, list(prompts[s.request]), [len(prompts[s.request]) - 1]) for s in live]
             first = True
@@ -126,8 +127,14 @@ class Generator:
                 else:
                     # decode: this step's input tokens go up from the host, the step is replayed
                     # as a graph, the selected tokens come back
-                    session.start([s.slot for s in live], [s.next_token for s in live],
-                                  [s.request for s in live], [s.steps for s in live])
+                    slots_now = [s.slot for s in live]
+                    if session.slots == slots_now and session_fresh:
+                        session.feed([s.next_token for s in live])
+                        session.steps_done = [s.steps for s in live]
+                    else:
+                        session.start(slots_now, [s.next_token for s in live],
+                                      [s.request for s in live], [s.steps for s in live])
+                        session_fresh = True
                     session.step_async(histories)
                     tokens, flags = session.read_tokens()
                 survivors = []

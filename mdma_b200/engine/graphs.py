@@ -67,6 +67,16 @@ class DecodeSession:
         self.seq_pos0[:B].copy_(h[cap:cap + B], non_blocking=True)
         self.seq_slot[:B].copy_(h[2 * cap:2 * cap + B], non_blocking=True)
 
+    def feed(self, tokens: Sequence[int]) -> None:
+        """The same sequences go on: only this step's input tokens go up (from pinned memory,
+        asynchronously; positions and slots are already on the device).  The caller has read the
+        previous step's tokens, so the staging buffer is free."""
+        B = len(self.slots)
+        if len(tokens) != B:
+            raise StepError(f"{len(tokens)} tokens for {B} live sequences")
+        self._host[:B] = torch.as_tensor(list(tokens), dtype=torch.int32)
+        self.ids[:B].copy_(self._host[:B], non_blocking=True)
+
     # ---- one step ----------------------------------------------------------
     def _body(self, B: int) -> None:
         ctx = self.ctx
