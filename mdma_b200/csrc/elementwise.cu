@@ -239,15 +239,6 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
     }
 }
 
-// y[i,:] = x[rows[i],:]
-template <typename T>
-__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows,
-                                   T* __restrict__ y, int width) {
-    const T* xr = x + (size_t)rows[blockIdx.x] * width;
-    T* yr = y + (size_t)blockIdx.x * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) yr[e] = xr[e];
-}
-
 // After a decode step: the sampled tokens become the next inputs and every
 // position moves on by one.
 __global__ void advance_decode_kernel(const int* __restrict__ tokens, int* __restrict__ ids,
@@ -355,15 +346,6 @@ int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const float* par
             tok_seq, tok_pos, seq_slot, inv_freq, (T*)k_cache, (T*)v_cache,
             page_table, max_pages, page_size, n_heads, n_kv_heads, head_dim, rotary_dim, interleaved, write_kv));
     MDMA_LAUNCH_OK("rope_cache_write");
-    return 0;
-}
-
-int mdma_gather_rows(const void* x, int dtype, const int* rows, void* y, int n_rows, int width,
-                     cudaStream_t stream) {
-    if (n_rows == 0) return 0;
-    MDMA_DISPATCH_DTYPE(dtype, T,
-        gather_rows_kernel<T><<<n_rows, 256, 0, stream>>>((const T*)x, rows, (T*)y, width));
-    MDMA_LAUNCH_OK("gather_rows");
     return 0;
 }
 

@@ -15,11 +15,10 @@ from __future__ import annotations
 
 from typing import Optional, Sequence
 
-import numpy as np
 import torch
 
 from .. import ops
-from ..sampling.params import SamplingParams, uniform
+from ..sampling.params import SamplingParams
 from .step import StepContext, StepError
 
 

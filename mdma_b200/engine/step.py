@@ -22,7 +22,7 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
-from ..cache import CacheFull, SequenceCache
+from ..cache import SequenceCache
 from ..config import load_config
 from ..parts.base import Runtime
 from ..weights import load_tensors, random_tensors, resident_dtype
@@ -202,10 +202,6 @@ class Engine:
 
     def release(self, slot: int) -> None:
         self.cache.release(slot)
-
-    @property
-    def max_slots_free(self) -> int:
-        return self.cache.slots.free_count
 
     def fits(self, sizes) -> bool:
         """Whether sequences of (prompt length, token budget) can be live together in an empty cache."""

@@ -140,13 +140,6 @@ def attention_simple(q: torch.Tensor, n_tokens: int, k_cache, v_cache, tok_seq, 
           _f(scale), _stream())
 
 
-def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
-    _need_cuda(x, rows, out)
-    assert x.is_contiguous() and out.is_contiguous() and rows.dtype == torch.int32
-    _call("core", "mdma_gather_rows", _ptr(x), _i(dtype_code(x.dtype)), _ptr(rows), _ptr(out),
-          _i(rows.numel()), _i(x.shape[1]), _stream())
-
-
 _argmax_scratch: dict = {}
 
 

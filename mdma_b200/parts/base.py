@@ -20,7 +20,6 @@ choices).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
 
 import torch
 

@@ -9,7 +9,7 @@ registered ones; nothing is approximated (the reference's rule for unknown
 """
 from __future__ import annotations
 
-from typing import Callable, Generic, Iterator, TypeVar
+from typing import Generic, Iterator, TypeVar
 
 T = TypeVar("T")
 

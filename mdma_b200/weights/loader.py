@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Iterable, Optional
+from typing import Optional
 
 import torch
 
