@@ -212,6 +212,28 @@ class SequenceCache:
             for g in self.groups:
                 g.trim(slot, self.lengths[slot])
 
+    def truncate(self, slot: int, length: int) -> None:
+        """Forget the tokens of `slot` from position `length` on (pages beyond go back to the free
+        list).  Refused when the cache holds fixed-size state or a windowed group has already given
+        pages of the kept part back: neither can be rewound (the reference's rule for its `rewind`,
+        src/kv_cache.rs:255-276)."""
+        old = self.lengths[slot]
+        if not 0 <= length <= old:
+            raise ValueError(f"cannot truncate a sequence of {old} tokens to {length}")
+        if self.states:
+            raise ValueError("a cache with fixed-size per-sequence state cannot be rewound")
+        for g in self.groups:
+            have = g.seq_pages.get(slot, {})
+            if g.need.window:
+                first_needed = max(0, length + 1 - g.need.window) // self.page_size
+                last = (length - 1) // self.page_size if length else -1
+                if any(p not in have for p in range(first_needed, last + 1)):
+                    raise ValueError("a windowed group has already released pages of the kept part")
+            keep_last = (length - 1) // self.page_size if length else -1
+            for p in [p for p in have if p > keep_last]:
+                g.pages.release(have.pop(p))
+        self.lengths[slot] = length
+
     def view(self, site: int, state_site: Optional[int] = None) -> KVView:
         """Pages of `site`; the fixed-size state of `state_site` (default: the same site)."""
         state = self.states.get(site if state_site is None else state_site)

@@ -82,11 +82,13 @@ class DecoderModel:
             part.bind(local, rt)
 
     def resident_bytes(self) -> int:
+        """Bytes of weights on the device; a tensor shared by two parts (a tied head) counts once."""
         seen, total = set(), 0
         for part in self.all_parts():
-            if id(part) not in seen:
-                seen.add(id(part))
-                total += part.resident_bytes()
+            for t in part.resident_tensors():
+                if t.data_ptr() not in seen:
+                    seen.add(t.data_ptr())
+                    total += t.numel() * t.element_size()
         return total
 
     # ---- forward ---------------------------------------------------------

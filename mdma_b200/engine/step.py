@@ -74,13 +74,15 @@ class StepContext:
 
 
 def memory_plan(model: DecoderModel, expected, dtype, max_tokens, max_slots, max_context, page_size,
-                chunk_tokens) -> dict:
-    """Bytes the engine will hold, from sizes alone (src/model/planning.rs:55-125)."""
+                chunk_tokens, stored: Optional[dict] = None) -> dict:
+    """Bytes the engine will hold, from sizes alone (src/model/planning.rs:55-125).  `stored` gives
+    the dtype each tensor has in the file (vectors stay as stored); without it bfloat16 is assumed."""
     elem = 4 if dtype == torch.float32 else 2
     weights = 0
     for name, ts in expected.items():
         n = int(np.prod(ts.shape))
-        weights += n * (4 if (ts.kind == "int" or dtype == torch.float32) else (2 if ts.kind == "matrix" else 4))
+        held = resident_dtype(ts, (stored or {}).get(name, torch.bfloat16), dtype)
+        weights += n * torch.empty((), dtype=held).element_size()
     cache = SequenceCache(model.kv_needs(), model.state_needs(), max_tokens, max_slots, max_context, dtype,
                           "meta", page_size, allocate=False)
     ws = sum(chunk_tokens * cols * (4 if kind == "f32" else elem)
@@ -98,8 +100,15 @@ def plan_only(model_dir: str, dtype="bfloat16", max_batch: int = 1, max_context:
     model = DecoderModel(spec)
     ctx = int(max_context or spec.max_positions)
     max_tokens = max_batch * (-(-ctx // page_size)) * page_size
+    stored = {}
+    try:
+        from ..weights import open_model_files
+        for sf in open_model_files(model_dir):
+            stored.update({n: e.dtype for n, e in sf.entries.items()})
+    except Exception:
+        stored = None                       # a folder without weights can still be planned
     return memory_plan(model, model.expected_tensors(), _DTYPES[dtype], max_tokens, max_batch, ctx,
-                       page_size, max(1, min(chunk_tokens, max_tokens)))
+                       page_size, max(1, min(chunk_tokens, max_tokens)), stored)
 
 
 class Engine:
@@ -149,7 +158,11 @@ class Engine:
 
         # ---- plan, then allocate ----------------------------------------
         expected = self.model.expected_tensors()
-        self.plan = self._plan(expected)
+        stored = None
+        if model_dir is not None:
+            from ..weights import open_model_files
+            stored = {n: e.dtype for sf in open_model_files(model_dir) for n, e in sf.entries.items()}
+        self.plan = self._plan(expected, stored)
         free, _total = torch.cuda.mem_get_info(self.device)
         if vram_bytes is not None:
             free = min(free, int(vram_bytes))
@@ -187,9 +200,29 @@ class Engine:
         self.forward_passes = 0
 
     # ---- planning ----------------------------------------------------------
-    def _plan(self, expected) -> dict:
+    def _plan(self, expected, stored=None) -> dict:
         return memory_plan(self.model, expected, self.dtype, self.max_tokens, self.max_slots,
-                           self.max_context, self.page_size, self.chunk_tokens)
+                           self.max_context, self.page_size, self.chunk_tokens, stored)
+
+    def held_bytes(self) -> dict:
+        """Bytes actually resident, in the plan's categories."""
+        cache = sum(g.k.numel() * g.k.element_size() * 2 + g.table_host.nbytes for g in self.cache.groups)
+        cache += sum(t.numel() * t.element_size() for t in self.cache.states.values())
+        ws = sum(t.numel() * t.element_size() for t in self.workspace.values())
+        return {"weights_bytes": self.model.resident_bytes(), "cache_bytes": cache, "workspace_bytes": ws}
+
+    def generate(self, prompts, max_tokens: int = 32, temperature: float = 0.0, seed: int = 0,
+                 stop_ids=None, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
+                 repetition_window: int = 64, use_graphs: bool = True):
+        """Generate from token-id prompts on this engine; see `mdma_b200.generate`."""
+        from ..sampling.params import SamplingParams
+        from ..sampling.sampler import DeviceSampler
+        from .generate import Generator
+        if getattr(self, "_generator", None) is None:
+            self._generator = Generator(self, DeviceSampler(self.vocab_size, self.max_slots, self.device), use_graphs)
+        params = SamplingParams(temperature, top_p, min_p, repetition_penalty, repetition_window, seed)
+        stop = self.spec.stop_token_ids if stop_ids is None else stop_ids
+        return self._generator.generate(prompts, max_tokens, params, stop)
 
     def decode_session(self, sampler, params=None):
         """A `DecodeSession` over this engine (decode steps replayed as CUDA graphs)."""

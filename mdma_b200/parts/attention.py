@@ -99,5 +99,5 @@ class Attention(Part):
                                  self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
         self.o_proj.accumulate(out, x, n)
 
-    def resident_bytes(self):
-        return self.qkv_proj.bytes() + self.o_proj.bytes()
+    def resident_tensors(self):
+        return [self.qkv_proj.w, self.o_proj.w]

@@ -56,5 +56,6 @@ class Part:
         """Take the device tensors named in tensor_specs()."""
         self.rt = rt
 
-    def resident_bytes(self) -> int:
-        return 0
+    def resident_tensors(self) -> list:
+        """The device tensors this part holds (for the memory account)."""
+        return []

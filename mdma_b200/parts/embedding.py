@@ -26,8 +26,8 @@ class Embedding(Part):
     def forward(self, ctx, ids, x):
         ops.embed_rows(self.weight, ids, x)
 
-    def resident_bytes(self):
-        return self.weight.numel() * self.weight.element_size()
+    def resident_tensors(self):
+        return [self.weight]
 
 
 @HEADS.register("lm_head")
@@ -46,5 +46,5 @@ class LMHead(Part):
     def forward(self, ctx, h_rows, logits, n_rows):
         self.proj.store(h_rows, logits, n_rows)
 
-    def resident_bytes(self):
-        return self.proj.bytes()
+    def resident_tensors(self):
+        return [self.proj.w]

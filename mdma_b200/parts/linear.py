@@ -43,6 +43,3 @@ class Linear:
     def swiglu(self, a, out, m):
         self._run(ops.GEMM_SWIGLU, a, out, m)
 
-    def bytes(self) -> int:
-        n = self.w.numel() * self.w.element_size()
-        return n * (2 if self.w2 is not None else 1)

@@ -38,5 +38,5 @@ class GatedMLP(Part):
         self.gate_up.swiglu(h, act, ctx.n_tokens)
         self.down.accumulate(act, x, ctx.n_tokens)
 
-    def resident_bytes(self):
-        return self.gate_up.bytes() + self.down.bytes()
+    def resident_tensors(self):
+        return [self.gate_up.w, self.gate_up.w2, self.down.w]

@@ -37,5 +37,5 @@ class RMSNorm(Part):
             ops_tensor.flush_pending(x.device)
         ops.rmsnorm(x, self.weight, self.eps, out, rows, n)
 
-    def resident_bytes(self):
-        return self.weight.numel() * self.weight.element_size()
+    def resident_tensors(self):
+        return [self.weight]

@@ -62,6 +62,9 @@ class Rotary(Part):
 
     fuses_pending = True        # adds up a deferred K-split projection itself
 
+    def resident_tensors(self):
+        return []                 # the frequency table is derived, not a weight
+
     def encode_and_store(self, ctx, qkv, n_heads, n_kv_heads, head_dim, view, write_kv):
         partial, splits, stride = None, 0, 0
         if self.rt.gemm == "tensor":

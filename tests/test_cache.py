@@ -119,3 +119,22 @@ def test_context_limit():
     s = c.acquire()
     assert "context" in c.can_extend({s: 129})
     assert c.can_extend({s: 128}) is None
+
+
+def test_truncate_gives_pages_back_and_refuses_what_cannot_be_rewound():
+    needs = [KVNeed(2, 16, 0)]
+    c = SequenceCache(needs, [None], 64 * 8, 2, 512, torch.float32, "cpu", page_size=64)
+    s = c.acquire()
+    c.extend({s: 300}); c.commit({s: 300})
+    free = c.groups[0].pages.free_count
+    c.truncate(s, 70)
+    assert c.length(s) == 70 and c.groups[0].pages.free_count == free + 3      # pages 2..4 returned
+    c.check()
+    c.extend({s: 100}); c.commit({s: 100})                                     # and it can grow again
+    assert c.length(s) == 170
+    with pytest.raises(ValueError):
+        c.truncate(s, 171)
+    stateful = make_cache()
+    t = stateful.acquire()
+    with pytest.raises(ValueError, match="state"):
+        stateful.truncate(t, 0)

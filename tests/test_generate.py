@@ -129,3 +129,43 @@ def test_missing_library_fails_loudly(monkeypatch):
     from mdma_b200 import ops
     with pytest.raises(build.BuildError):
         ops.argmax(torch.zeros(1, 4, device="cuda:0"), torch.zeros(1, dtype=torch.int32, device="cuda:0"))
+
+
+def test_plan_equals_what_is_held():
+    """The memory plan, made from sizes alone, is what the engine then holds (the reference's rule:
+    src/model/arch/llama/tests.rs:8-66, src/model/planning/tests.rs:6-30)."""
+    from mdma_b200.engine import Engine
+    from mdma_b200.engine.step import plan_only
+    for cfg, seed, wdtype, dtype in ((TINY_A, 0, torch.float32, "float32"), (TINY_B, 1, torch.bfloat16, "bfloat16"),
+                                     (TINY_C, 2, torch.float32, "bfloat16")):
+        d, _, _ = make_model(cfg, seed, wdtype)
+        eng = Engine(d, dtype=dtype, max_batch=3, max_context=128)
+        held = eng.held_bytes()
+        for key in ("weights_bytes", "cache_bytes", "workspace_bytes"):
+            assert eng.plan[key] == held[key], (key, eng.plan[key], held[key])
+        alone = plan_only(d, dtype=dtype, max_batch=3, max_context=128)
+        assert alone["weights_bytes"] == held["weights_bytes"] and alone["cache_bytes"] == held["cache_bytes"]
+
+
+def test_graph_replay_equals_eager():
+    """Decode steps replayed as CUDA graphs give the tokens of the eager path, greedy and sampled
+    (the reference asks the same of its graph decoder: src/backend/test_support/graph.rs:16-75)."""
+    import mdma_b200
+    for cfg, seed, wdtype in ((TINY_A, 0, torch.float32), (TINY_B, 1, torch.bfloat16)):
+        d, _, _ = make_model(cfg, seed, wdtype)
+        prompts = prompts_for(cfg, (5, 11, 17, 3), 0)
+        for dtype in ("float32", "bfloat16"):
+            for kw in (dict(temperature=0.0), dict(temperature=0.8, top_p=0.9, repetition_penalty=1.1, seed=5)):
+                a = mdma_b200.generate(d, prompts, max_tokens=12, dtype=dtype, max_batch=4, use_graphs=True, **kw)
+                b = mdma_b200.generate(d, prompts, max_tokens=12, dtype=dtype, max_batch=4, use_graphs=False, **kw)
+                assert [o.tokens for o in a] == [o.tokens for o in b], (dtype, kw)
+
+
+def test_engine_generate_method():
+    from mdma_b200.engine import Engine
+    d, c, tensors = make_model(TINY_A, 0, torch.float32)
+    eng = Engine(d, dtype="float32", max_batch=2, max_context=64)
+    p = prompts_for(TINY_A, (6, 9), 3)
+    outs = eng.generate(p, max_tokens=5)
+    assert [o.tokens for o in outs] == [plain_generate(c, tensors, q, 5) for q in p]
+    assert eng.generate(p, max_tokens=5)[0].tokens == outs[0].tokens       # slots were given back: it runs again
