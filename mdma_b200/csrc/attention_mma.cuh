@@ -468,8 +468,10 @@ attention_decode_kernel(const AttnParams p) {
 // tile load, completion on the warp's own mbarrier) instead of 16-byte cp.async copies, whose address
 // arithmetic was two thirds of the instructions.  Needs page_size to be a multiple of KB.  A tile is
 // stored as halves of 64 head elements: [KB keys x 128 bytes] with the 128-byte swizzle.
-template <int DMAX, int KB>
-__global__ void __launch_bounds__(kAttnThreads, 3)
+// NW warps per block: four (three blocks per SM) when the keys are split over blocks, eight when one
+// block takes all keys of a short context, which needs no merge kernel.
+template <int DMAX, int KB, int NW>
+__global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : 1)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const AttnParams p) {
     constexpr int kChunks = DMAX / 8;
@@ -479,15 +481,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const uint32_t s0 = (uint32_t)__cvta_generic_to_shared(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t sK = s0 + warp * 2 * kTile, sV = sK + kTile;      // tiles first: they need 1024-byte alignment
-    const uint32_t sQ = s0 + 4 * 2 * kTile;              // 16 rows x DMAX
+    const uint32_t sQ = s0 + NW * 2 * kTile;              // 16 rows x DMAX
     const uint32_t bars = sQ + 16 * DMAX * 2;
     const uint32_t kbar = bars + warp * 16, vbar = kbar + 8;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 4 * 2 * kTile + 16 * DMAX * 2 + 64);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + NW * 2 * kTile + 16 * DMAX * 2 + NW * 16);
     auto kv_offset = [](int row, int chunk) -> uint32_t {      // 16-byte chunk of a key row inside a tile
         return (uint32_t)((chunk >> 3) * kHalf + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
     };
     if (threadIdx.x == 0) {
-        for (int w = 0; w < 4; ++w) { ptx::mbar_init(bars + w * 16, 1); ptx::mbar_init(bars + w * 16 + 8, 1); }
+        for (int w = 0; w < NW; ++w) { ptx::mbar_init(bars + w * 16, 1); ptx::mbar_init(bars + w * 16 + 8, 1); }
         *abort_flag = (s0 & 1023u) ? 1 : 0;
         ptx::fence_mbar_init();
     }
@@ -517,7 +519,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (*abort_flag != 0) blk = b1;
     if (blk < b1 && lane == 0) { load_tile(&map_k, sK, kbar, blk); load_tile(&map_v, sV, vbar, blk); }
     // Q rows (heads of the group) -> shared, zero beyond G and beyond D
-    for (int i = threadIdx.x; i < 16 * kChunks; i += kAttnThreads) {
+    for (int i = threadIdx.x; i < 16 * kChunks; i += NW * 32) {
         const int r = i / kChunks, c = i % kChunks;
         const bool valid = r < G && c < d_chunks;
         const __nv_bfloat16* src = p.q + (size_t)token * p.q_stride + (size_t)(kvh * G + (valid ? r : 0)) * D + (valid ? c : 0) * 8;
@@ -539,7 +541,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     for (int n = 0; n < DMAX / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
-    for (; blk < b1; blk += 4) {
+    for (; blk < b1; blk += NW) {
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(kbar, phase, abort_flag))) break;     // this tile's K has landed
         float s[KB / 8][4];
 #pragma unroll
@@ -558,8 +560,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             }
         }
         __syncwarp();
-        const bool more = blk + 4 < b1;
-        if (more && lane == 0) load_tile(&map_k, sK, kbar, blk + 4);     // K buffer is free: fetch the next tile's keys
+        const bool more = blk + NW < b1;
+        if (more && lane == 0) load_tile(&map_k, sK, kbar, blk + NW);     // K buffer is free: fetch the next tile's keys
         const int key_base = blk * KB + (lane & 3) * 2;
         float mx_lo = m_lo, mx_hi = m_hi;
 #pragma unroll
@@ -611,7 +613,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             }
         }
         __syncwarp();
-        if (more && lane == 0) load_tile(&map_v, sV, vbar, blk + 4);
+        if (more && lane == 0) load_tile(&map_v, sV, vbar, blk + NW);
         phase ^= 1u;
     }
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -637,14 +639,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < G * D; i += kAttnThreads) {
+    for (int i = threadIdx.x; i < G * D; i += NW * 32) {
         const int r = i / D, d = i % D;
         float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) m = fmaxf(m, comb[((size_t)w * 16 + r) * kRowF + DMAX]);
+        for (int w = 0; w < NW; ++w) m = fmaxf(m, comb[((size_t)w * 16 + r) * kRowF + DMAX]);
         float l = 0.f, acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < NW; ++w) {
             const float mw = comb[((size_t)w * 16 + r) * kRowF + DMAX];
             if (mw != -INFINITY) {
                 const float f = exp2f(mw - m);
@@ -764,17 +766,21 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
         CUtensorMap mk, mv;
         if (int rc = make_cache_map(&mk, k_cache, n_pages, page_size, n_kv_heads, head_dim, kDecodeKeys)) return rc;
         if (int rc = make_cache_map(&mv, v_cache, n_pages, page_size, n_kv_heads, head_dim, kDecodeKeys)) return rc;
-        if (head_dim <= 64) {
-            constexpr int bytes = 4 * 2 * kDecodeKeys * 64 * 2 + 16 * 64 * 2 + 128;
-            static bool once = false;
-            if (!once) { cudaFuncSetAttribute(attention_decode_tma_kernel<64, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
-            launch_chained(attention_decode_tma_kernel<64, kDecodeKeys>, grid, dim3(kAttnThreads), bytes, stream, mk, mv, p);
-        } else {
-            constexpr int bytes = 4 * 2 * kDecodeKeys * 128 * 2 + 16 * 128 * 2 + 128;
-            static bool once = false;
-            if (!once) { cudaFuncSetAttribute(attention_decode_tma_kernel<128, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
-            launch_chained(attention_decode_tma_kernel<128, kDecodeKeys>, grid, dim3(kAttnThreads), bytes, stream, mk, mv, p);
-        }
+        // eight warps when one block per (sequence, kv head) takes all keys, four when keys are split
+        auto launch = [&](auto kernel, int nw, int dmax) -> int {
+            const int bytes = nw * 2 * kDecodeKeys * dmax * 2 + 16 * dmax * 2 + nw * 16 + 64;
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+            if (e != cudaSuccess) return fail("attention: cannot reserve %d bytes of shared memory: %s", bytes, cudaGetErrorString(e));
+            e = launch_chained(kernel, grid, dim3(nw * 32), bytes, stream, mk, mv, p);
+            if (e != cudaSuccess) return fail("attention: launch failed: %s", cudaGetErrorString(e));
+            return 0;
+        };
+        int rc;
+        if (splits == 1 && head_dim <= 64) rc = launch(attention_decode_tma_kernel<64, kDecodeKeys, 8>, 8, 64);
+        else if (splits == 1) rc = launch(attention_decode_tma_kernel<128, kDecodeKeys, 8>, 8, 128);
+        else if (head_dim <= 64) rc = launch(attention_decode_tma_kernel<64, kDecodeKeys, 4>, 4, 64);
+        else rc = launch(attention_decode_tma_kernel<128, kDecodeKeys, 4>, 4, 128);
+        if (rc) return rc;
     } else if (max_new == 1 && p.group <= 16) {
         // one token per sequence: the decode kernel (no padding rows beyond one 16-row tile)
         if (head_dim <= 64) {

@@ -39,6 +39,7 @@ class DecodeSession:
         self.ctx = StepContext(engine.rt, engine.workspace)
         self.steps_done: list[int] = []
         self.launches_per_step = 0          # kernels in one step (counted at the eager first run)
+        self._bucket = engine.max_context
 
     @property
     def graph_safe(self) -> bool:
@@ -82,7 +83,7 @@ class DecodeSession:
         ctx.ids, ctx.tok_pos, ctx.seq_slot, ctx.seq_pos0 = self.ids[:B], self.tok_pos[:B], self.seq_slot[:B], self.seq_pos0[:B]
         ctx.tok_seq, ctx.seq_start, ctx.want_rows = self.arange[:B], self.arange[:B + 1], self.arange[:B]
         ctx.n_tokens = ctx.n_seqs = ctx.n_want = B
-        ctx.max_new, ctx.max_len = 1, self.engine.max_context
+        ctx.max_new, ctx.max_len = 1, self._bucket
         ctx.decode_only = True
         ctx.host_seq_new, ctx.host_seq_pos0, ctx.host_seq_slot = [1] * B, None, list(self.slots)
         self.engine.model.forward(ctx, self.engine.cache, self.logits[:B])
@@ -109,8 +110,12 @@ class DecodeSession:
         p = self.params
         if p.temperature > 0.0 or (p.repetition_penalty != 1.0 and p.repetition_window > 0):
             self.sampler.stage_inputs(p, self.requests, self.steps_done, histories)
+        # kernels choose their grids from an upper bound of the context: the live maximum rounded up
+        # to 1024, so a graph stays valid until a sequence grows past its bucket
+        longest = max(self.engine.cache.length(s_) for s_ in self.slots) + 1
+        self._bucket = min(self.engine.max_context, -(-longest // 1024) * 1024)
         if use_graph and self.graph_safe:
-            g = self.graphs.get(B)
+            g = self.graphs.get((B, self._bucket))
             if g is None:
                 # The first step at this batch size runs eagerly (it loads kernels and sizes
                 # scratch); the same chain is then captured, without running, for the next ones.
@@ -120,7 +125,7 @@ class DecodeSession:
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     self._body(B)
-                self.graphs[B] = g
+                self.graphs[(B, self._bucket)] = g
             else:
                 g.replay()
         else:

@@ -136,12 +136,13 @@ def attention_splits(n_seqs: int, max_new: int, max_len: int, n_heads: int, n_kv
     group = n_heads // n_kv_heads
     key_blocks = max(1, -(-max_len // 64))
     if max_new == 1 and group <= 16:
-        # decode kernel: a block's four warps already take four key blocks at a time
+        # decode kernel: a block's warps each take 32-key tiles in turn.  Short contexts: one block of
+        # eight warps per (sequence, kv head), no merge kernel; else four warps and a K split.
         blocks = n_seqs * n_kv_heads
-        if blocks >= 2 * sms:
+        if max_len <= 1024 or blocks >= 2 * sms:
             return 1
         rounds = -(-max_len // (32 * 4))           # four warps x 32 keys per round
-        return max(1, min(-(-3 * sms // blocks), rounds, 32))
+        return max(2, min(-(-3 * sms // blocks), rounds, 32))
     tile_tokens = max(1, 64 // group)
     blocks = -(-max_new // tile_tokens) * n_seqs * n_kv_heads
     if blocks >= 2 * sms:
