@@ -272,10 +272,16 @@ template <int MODE>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                 const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    // Persistent: the grid holds at most one pair per two SMs and every pair walks over output tiles
+    // (tile, tile + pairs, ...).  The shared-memory ring runs on across tiles, and with one weight
+    // matrix the accumulator has two buffers in tensor memory, so a tile's epilogue runs under the
+    // next tile's MMAs.
     using S = Tc2Smem<MODE>;
     constexpr int kStages = S::kStages;
     constexpr bool kDual = MODE == kTcSwiGLU;
     constexpr int BN = 256;
+    constexpr int kBufs = kDual ? 1 : 2;                   // accumulator buffers of 256 (512) columns
+    constexpr int kBufCols = kDual ? 512 : 256;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - ptx::smem_addr(smem_raw));
@@ -283,27 +289,29 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const uint32_t bar0 = base + kStages * S::kStage;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
-    const uint32_t acc_bar = bar0 + 8u * (2 * kStages);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 1);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages + 2);
+    auto acc_full = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages + 5);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = (int)ptx::cluster_rank();
-    const int f0 = (blockIdx.x / 2) * 256 + rank * 128;        // this block's weight rows
-    const int t0 = blockIdx.y * BN;                             // the pair's tokens; this block loads t0 + rank*128 ...
+    const int n_pairs = gridDim.x / 2, pair = blockIdx.x / 2;
+    const int f_tiles = (p.n_features + 255) / 256, t_tiles = (p.n_tokens + BN - 1) / BN;
+    const int n_tiles = f_tiles * t_tiles;
     const int n_kb = p.k_blocks;
 
     // This kernel takes no part in programmatic dependent launch: launched early next to the tail of
-    // another kernel it stalled now and then (seen with the rotary, norm and attention kernels before
-    // it); it is used for many tokens, where a launch gap is nothing against its run time.
+    // another kernel it stalled now and then; it is used for many tokens, where a launch gap is
+    // nothing against its run time.
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-        ptx::mbar_init(acc_bar, 1);
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(acc_full(b), 1); ptx::mbar_init(acc_empty(b), 8); }   // 4 epilogue warps x 2 blocks
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
-        ptx::tmem_alloc_pair(ptx::smem_addr((const void*)tmem_slot), S::kTmemCols);
+        ptx::tmem_alloc_pair(ptx::smem_addr((const void*)tmem_slot), 512);
         ptx::tmem_relinquish_pair();
     }
     ptx::tc_fence_before_sync();
@@ -316,52 +324,69 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         ptx::prefetch_tensormap(&map_w);
         ptx::prefetch_tensormap(&map_x);
         if (kDual) ptx::prefetch_tensormap(&map_w2);
-        int issued = 0;
-        for (int i = 0; i < n_kb; ++i) {
-            const int s = i % kStages;
-            if (!ptx::mbar_wait(empty_bar(s), ((i / kStages) & 1) ^ 1, abort_flag)) break;
-            const uint32_t stage = base + s * S::kStage;
-            const uint32_t lead_full = ptx::cluster_map(full_bar(s), 0);
-            if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 2 * S::kStage);       // both blocks' bytes
-            const int k = i * kBK;
-            ptx::tma_load_2d_pair(stage, &map_w, lead_full, k, f0);
-            if (kDual) ptx::tma_load_2d_pair(stage + S::kA, &map_w2, lead_full, k, f0);
-            ptx::tma_load_2d_pair(stage + S::kA * (kDual ? 2 : 1), &map_x, lead_full, k, t0 + rank * 128);
-            ++issued;
+        int it = 0;                        // stage uses so far, across tiles
+        bool ok = true;
+        for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+            const int f0 = (tile / t_tiles) * 256 + rank * 128;      // token tiles of one feature tile run together
+            const int t0 = (tile % t_tiles) * BN + rank * 128;
+            for (int i = 0; i < n_kb; ++i, ++it) {
+                const int s = it % kStages;
+                if (!ptx::mbar_wait(empty_bar(s), ((it / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                const uint32_t stage = base + s * S::kStage;
+                const uint32_t lead_full = ptx::cluster_map(full_bar(s), 0);
+                if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 2 * S::kStage);       // both blocks' bytes
+                const int k = i * kBK;
+                ptx::tma_load_2d_pair(stage, &map_w, lead_full, k, f0);
+                if (kDual) ptx::tma_load_2d_pair(stage + S::kA, &map_w2, lead_full, k, f0);
+                ptx::tma_load_2d_pair(stage + S::kA * (kDual ? 2 : 1), &map_x, lead_full, k, t0);
+            }
         }
-        (void)issued;
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ---- MMA issuer (leading block only) ----------------------------------------------
         constexpr uint32_t idesc = ptx::idesc_bf16_f32(256, BN);
+        int it = 0, j = 0;
         bool ok = true;
-        for (int i = 0; i < n_kb && ok; ++i) {
-            const int s = i % kStages;
-            ok = ptx::mbar_wait(full_bar(s), (i / kStages) & 1, abort_flag);
+        for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++j) {
+            const int buf = j % kBufs;
+            // the buffer's previous tile must have been read out by both blocks' epilogues
+            ok = ptx::mbar_wait(acc_empty(buf), (((j / kBufs) & 1) ^ 1), abort_flag);
             if (!ok) break;
             ptx::tc_fence_after_sync();
-            const uint32_t stage = base + s * S::kStage;
-            const uint32_t a_addr = stage, b_addr = stage + S::kA * (kDual ? 2 : 1);
+            const uint32_t acc_addr = tmem_base + buf * kBufCols;
+            for (int i = 0; i < n_kb; ++i, ++it) {
+                const int s = it % kStages;
+                ok = ptx::mbar_wait(full_bar(s), (it / kStages) & 1, abort_flag);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t stage = base + s * S::kStage;
+                const uint32_t a_addr = stage, b_addr = stage + S::kA * (kDual ? 2 : 1);
 #pragma unroll
-            for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-                const uint64_t b_desc = ptx::smem_desc_sw128(b_addr + kk * kUmmaK * 2);
-                const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-                ptx::mma_bf16_ss_pair(tmem_base, ptx::smem_desc_sw128(a_addr + kk * kUmmaK * 2), b_desc, idesc, acc);
-                if (kDual)
-                    ptx::mma_bf16_ss_pair(tmem_base + BN, ptx::smem_desc_sw128(a_addr + S::kA + kk * kUmmaK * 2),
-                                          b_desc, idesc, acc);
+                for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+                    const uint64_t b_desc = ptx::smem_desc_sw128(b_addr + kk * kUmmaK * 2);
+                    const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+                    ptx::mma_bf16_ss_pair(acc_addr, ptx::smem_desc_sw128(a_addr + kk * kUmmaK * 2), b_desc, idesc, acc);
+                    if (kDual)
+                        ptx::mma_bf16_ss_pair(acc_addr + BN, ptx::smem_desc_sw128(a_addr + S::kA + kk * kUmmaK * 2),
+                                              b_desc, idesc, acc);
+                }
+                ptx::mma_commit_pair(empty_bar(s), 3);      // frees the stage in both blocks
             }
-            ptx::mma_commit_pair(empty_bar(s), 3);      // frees the stage in both blocks
+            ptx::mma_commit_pair(acc_full(buf), 3);         // both blocks' accumulators of this tile are complete
         }
-        ptx::mma_commit_pair(acc_bar, 3);               // both blocks' accumulators are complete
-    }
-    if (warp >= 2) {
-        // ---- epilogue: each block stores its own 128 features x 256 tokens ---------------------
+    } else if (warp >= 2) {
+        // ---- epilogue: each block stores its own 128 features x 256 tokens of every tile ----------
         const int quad = warp & 3;
-        const int f = f0 + quad * 32 + lane;
-        const bool ok = ptx::mbar_wait(acc_bar, 0, abort_flag);
-        ptx::tc_fence_after_sync();
-        if (ok && n_kb > 0) {
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const uint32_t lead_empty[2] = {ptx::cluster_map(acc_empty(0), 0), ptx::cluster_map(acc_empty(1), 0)};
+        int j = 0;
+        bool ok = true;
+        for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++j) {
+            const int buf = j % kBufs;
+            const int f = (tile / t_tiles) * 256 + rank * 128 + quad * 32 + lane;
+            const int t0 = (tile % t_tiles) * BN;
+            ok = __all_sync(0xffffffffu, ptx::mbar_wait(acc_full(buf), (j / kBufs) & 1, abort_flag));
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t lane_addr = tmem_base + buf * kBufCols + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 if (t0 + c >= p.n_tokens) break;
@@ -374,29 +399,33 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         float* o = reinterpret_cast<float*>(p.out) + (size_t)(t0 + c) * p.ldo + f;
                         float old[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) old[j] = j < valid ? o[(size_t)j * p.ldo] : 0.f;
+                        for (int q = 0; q < 16; ++q) old[q] = q < valid ? o[(size_t)q * p.ldo] : 0.f;
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) if (j < valid) o[(size_t)j * p.ldo] = old[j] + v[j];
+                        for (int q = 0; q < 16; ++q) if (q < valid) o[(size_t)q * p.ldo] = old[q] + v[q];
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (j >= valid) break;
-                            const int t = t0 + c + j;
-                            float r = v[j];
-                            if (MODE == kTcSwiGLU) r = r / (1.0f + __expf(-r)) * u[j];
+                        for (int q = 0; q < 16; ++q) {
+                            if (q >= valid) break;
+                            const int t = t0 + c + q;
+                            float r = v[q];
+                            if (MODE == kTcSwiGLU) r = r / (1.0f + __expf(-r)) * u[q];
                             if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + f] = r;
                             else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(r);
                         }
                     }
                 }
             }
+            // this warp has read its part of the buffer: tell the leading block's MMA thread
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(lead_empty[buf]);
         }
     }
     ptx::tc_fence_before_sync();
     ptx::cluster_sync();                   // neither block leaves (or frees tensor memory) while the other may still use it
     if (warp == 1) {
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc_pair(tmem_base, S::kTmemCols);
+        ptx::tmem_dealloc_pair(tmem_base, 512);
     }
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 3);
 }
@@ -537,7 +566,17 @@ static int run_tc2(const void* x, int ldx, const void* w, const void* w2, int K,
     if (int rc = make_map_2d(&mx, x, (uint64_t)p.n_tokens, (uint64_t)K, (uint64_t)ldx * 2, 128)) return rc;
     p.cluster = 1;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(((p.n_features + 255) / 256) * 2, (p.n_tokens + 255) / 256, 1);
+    // persistent: one pair per two SMs at most
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count < 2) sm_count = 2;
+    }
+    const long tiles = (long)((p.n_features + 255) / 256) * ((p.n_tokens + 255) / 256);
+    const int pairs = (int)(tiles < sm_count / 2 ? tiles : sm_count / 2);
+    cfg.gridDim = dim3(pairs * 2, 1, 1);
     cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = S::kBytes; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;

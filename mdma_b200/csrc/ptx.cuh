@@ -76,6 +76,10 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
     return remote;
 }
+// Arrives on an mbarrier that may live in another block of the cluster (`remote` from cluster_map).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
 __device__ __forceinline__ void cluster_store_f32(uint32_t remote, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }

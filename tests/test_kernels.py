@@ -415,7 +415,9 @@ def test_gemm_tensor_cluster_split(cluster, M, N, K, mode):
 
 
 @pytest.mark.parametrize("M,N,K,mode", [(256, 256, 64, 0), (300, 520, 1032, 0), (1000, 264, 512, 1), (257, 384, 640, 2),
-                                        (2048, 1024, 2048, 2), (130, 100, 72, 0)])
+                                        (2048, 1024, 2048, 2), (130, 100, 72, 0),
+                                        # more tiles than block pairs: every pair walks over several tiles
+                                        (1100, 5000, 256, 0), (1100, 5000, 256, 1), (1100, 5000, 256, 2), (2300, 8200, 192, 1)])
 def test_gemm_tensor_block_pairs(M, N, K, mode):
     """The two-block kernel (cta_group::2): a pair covers 256 features x 256 tokens."""
     from mdma_b200 import ops_tensor
