@@ -14,6 +14,8 @@ from .csrc import build as _build
 from .ops import KernelError, _call, _f, _i, _need_cuda, _ptr, _stream
 
 _state: dict = {}
+# MDMA_EVEN_SPLIT=0: the block-pair GEMM gives every pair whole tiles only (for comparisons).
+EVEN_SPLIT = os.environ.get("MDMA_EVEN_SPLIT", "1") != "0"
 
 
 def _device_state(device: torch.device) -> dict:
@@ -21,6 +23,7 @@ def _device_state(device: torch.device) -> dict:
     if st is None:
         st = {"pending": None,
               "status": torch.zeros(4, dtype=torch.int32, device=device),
+              "sk_flags": torch.zeros(512, dtype=torch.int32, device=device),
               "scratch": torch.empty(1 << 20, dtype=torch.float32, device=device),
               "sms": torch.cuda.get_device_properties(device).multi_processor_count}
         _state[device.index] = st
@@ -112,6 +115,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
         bn = bn or pbn
         splits = splits or psplits
     need = splits * M * N if splits > 1 else 0
+    if bn == 512:
+        need = 148 * 2 * 256 * 128          # partial tiles of the block-pair kernel's even K-block split
     if need > st["scratch"].numel():
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("split-K scratch is too small and cannot grow during graph capture")
@@ -120,7 +125,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
     _call("tensor", "mdma_gemm_tc", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), _ptr(out),
           _i(int(out.dtype == torch.float32)), _i(out.stride(0)), _i(M), _i(N), _i(K), _i(bn), _i(splits),
           _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]),
-          _i(int(defer)), ctypes.byref(used), _stream(),
+          _i(int(defer)), ctypes.byref(used), _ptr(st["sk_flags"]) if EVEN_SPLIT else None, _stream(),
           launches=1 if (splits == 1 or defer) else 2)
     if defer and used.value > 1:
         st["pending"] = Pending(out, mode, used.value, M, N)

@@ -417,7 +417,9 @@ def test_gemm_tensor_cluster_split(cluster, M, N, K, mode):
 @pytest.mark.parametrize("M,N,K,mode", [(256, 256, 64, 0), (300, 520, 1032, 0), (1000, 264, 512, 1), (257, 384, 640, 2),
                                         (2048, 1024, 2048, 2), (130, 100, 72, 0),
                                         # more tiles than block pairs: every pair walks over several tiles
-                                        (1100, 5000, 256, 0), (1100, 5000, 256, 1), (1100, 5000, 256, 2), (2300, 8200, 192, 1)])
+                                        (1100, 5000, 256, 0), (1100, 5000, 256, 1), (1100, 5000, 256, 2), (2300, 8200, 192, 1),
+                                        # tiles shared by two pairs (K blocks split evenly), several K blocks per part
+                                        (1100, 5000, 1032, 0), (1100, 5000, 1032, 1), (700, 9000, 2048, 2), (2048, 4096, 4096, 0)])
 def test_gemm_tensor_block_pairs(M, N, K, mode):
     """The two-block kernel (cta_group::2): a pair covers 256 features x 256 tokens."""
     from mdma_b200 import ops_tensor
@@ -439,6 +441,9 @@ def test_gemm_tensor_block_pairs(M, N, K, mode):
         want = ref if mode == 0 else ref / (1 + torch.exp(-ref)) * (a[:M].double() @ w2.double().t())
         close(out[:M], want, 1e-2, 1e-2)
         assert bool((out[M:] == 9.0).all())
+        again = torch.full_like(out, 9.0)       # a second call finds the scratch and its flags as the first left them
+        ops_tensor.gemm(a, w, again, mode, w2 if mode == 2 else None, M, bn=512, splits=1)
+        assert torch.equal(out, again)
     ops_tensor.check_status(torch.device(DEV))
 
 
