@@ -239,6 +239,68 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
     }
 }
 
+// The same for many tokens of bfloat16 in the split-half layout, no partial sums: 16-byte accesses,
+// eight pairs (d, d + rotary_dim/2) per thread and step.  One block per token.
+__global__ void rope_cache_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, int row_stride,
+                                            const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                            const int* __restrict__ seq_slot, const float* __restrict__ inv_freq,
+                                            __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                            const int* __restrict__ page_table, int max_pages, int page_size,
+                                            int n_heads, int n_kv_heads, int head_dim, int rotary_dim, int write_kv) {
+    extern __shared__ float sc[];                  // [rotary_dim/2] sines, then cosines
+    chain_release();
+    chain_wait();
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = rotary_dim / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        sc[i] = s; sc[half + i] = c;
+    }
+    __syncthreads();
+    __nv_bfloat16* row = qkv + (size_t)t * row_stride;
+    size_t cache_row = 0;
+    if (write_kv) {
+        const int slot = seq_slot[tok_seq[t]];
+        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+        cache_row = ((size_t)page * page_size + (size_t)(pos % page_size)) * n_kv_heads;
+    }
+    const int rot_heads = n_heads + (write_kv ? n_kv_heads : 0);
+    const int groups = half / 8;                   // groups of eight pairs per head
+    for (int i = threadIdx.x; i < rot_heads * groups; i += blockDim.x) {
+        const int h = i / groups, d = (i % groups) * 8;
+        const __nv_bfloat16* src = row + (size_t)h * head_dim;
+        __nv_bfloat16* dst = h < n_heads ? row + (size_t)h * head_dim : k_cache + (cache_row + (h - n_heads)) * head_dim;
+        const uint4 lo = *reinterpret_cast<const uint4*>(src + d), hi = *reinterpret_cast<const uint4*>(src + d + half);
+        const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(&lo);
+        const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&hi);
+        uint4 olo, ohi;
+        __nv_bfloat16* oa = reinterpret_cast<__nv_bfloat16*>(&olo);
+        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&ohi);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float x0 = __bfloat162float(a[q]), x1 = __bfloat162float(b[q]);
+            const float sn = sc[d + q], cs = sc[half + d + q];
+            oa[q] = __float2bfloat16_rn(x0 * cs - x1 * sn);
+            ob[q] = __float2bfloat16_rn(x0 * sn + x1 * cs);
+        }
+        *reinterpret_cast<uint4*>(dst + d) = olo;
+        *reinterpret_cast<uint4*>(dst + d + half) = ohi;
+    }
+    if (!write_kv) return;
+    // not rotated: k beyond rotary_dim, and v (q beyond rotary_dim stays where it is)
+    const int tail8 = (head_dim - rotary_dim) / 8;
+    for (int i = threadIdx.x; i < n_kv_heads * tail8; i += blockDim.x) {
+        const int h = i / tail8, d = rotary_dim + (i % tail8) * 8;
+        *reinterpret_cast<uint4*>(k_cache + (cache_row + h) * head_dim + d) =
+            *reinterpret_cast<const uint4*>(row + (size_t)(n_heads + h) * head_dim + d);
+    }
+    const __nv_bfloat16* v_src = row + (size_t)(n_heads + n_kv_heads) * head_dim;
+    for (int i = threadIdx.x; i < n_kv_heads * head_dim / 8; i += blockDim.x)
+        *reinterpret_cast<uint4*>(v_cache + cache_row * head_dim + (size_t)i * 8) = *reinterpret_cast<const uint4*>(v_src + (size_t)i * 8);
+}
+
 // After a decode step: the sampled tokens become the next inputs and every
 // position moves on by one.
 __global__ void advance_decode_kernel(const int* __restrict__ tokens, int* __restrict__ ids,
@@ -332,6 +394,16 @@ int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const float* par
     MDMA_REQUIRE(!write_kv || (page_table && page_size > 0 && max_pages > 0), "rope_cache_write: no cache pages");
     MDMA_REQUIRE(splits >= 0 && (splits == 0 || partial), "rope_cache_write: partial sums need a pointer");
     if (n_tokens == 0) return 0;
+    const bool aligned16 = ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0;
+    if (n_tokens >= 256 && dtype == kBF16 && splits == 0 && !interleaved && rotary_dim % 16 == 0 && head_dim % 8 == 0 &&
+        row_stride % 8 == 0 && aligned16) {
+        using B = __nv_bfloat16;
+        launch_chained(rope_cache_write_vec_kernel, dim3(n_tokens), dim3(256), (size_t)rotary_dim * sizeof(float), stream,
+            (B*)qkv, row_stride, tok_seq, tok_pos, seq_slot, inv_freq, (B*)k_cache, (B*)v_cache,
+            page_table, max_pages, page_size, n_heads, n_kv_heads, head_dim, rotary_dim, write_kv);
+        MDMA_LAUNCH_OK("rope_cache_write");
+        return 0;
+    }
     // about 300 blocks at least: few tokens get several blocks per row, many tokens one
     const int total_heads = n_heads + (write_kv ? 2 * n_kv_heads : 0);
     int per_token = n_tokens >= 300 ? 1 : (n_tokens <= 128 ? total_heads : (300 + n_tokens - 1) / n_tokens);

@@ -147,6 +147,50 @@ def test_rope_cache_write(dtype, layout, hd, rot):
     assert bool((kc.cpu()[mask] == 0).all()) and bool((vc.cpu()[mask] == 0).all())   # nothing else written
 
 
+@pytest.mark.parametrize("hd,rot,H,K", [(128, 128, 5, 2), (80, 64, 3, 3), (64, 32, 4, 1)])
+def test_rope_cache_write_many_tokens(hd, rot, H, K):
+    """300+ bfloat16 tokens take the kernel with 16-byte accesses: two sequences whose pages are scattered,
+    one starting far into its context; every other cache row stays untouched."""
+    ops = ops_mod()
+    torch.manual_seed(1)
+    page, max_pages = 16, 1300
+    lens, starts = [170, 150], [0, 20000]
+    pos = [starts[s] + i for s in range(2) for i in range(lens[s])]
+    seq = [s for s in range(2) for _ in range(lens[s])]
+    T = len(pos)
+    qkv = torch.randn(T + 1, (H + 2 * K) * hd, device=DEV).bfloat16()
+    orig = qkv.clone()
+    inv = plain_inv_freq(rot, 5e5, None).to(DEV)
+    n_pages = 40
+    kc, vc = paged_cache(n_pages, page, K, hd, torch.bfloat16)
+    order = torch.randperm(n_pages).tolist()
+    table = torch.zeros(2, max_pages, dtype=torch.int32)
+    cur = 0
+    for s in range(2):
+        for pg in range(starts[s] // page, (starts[s] + lens[s] - 1) // page + 1):
+            table[s, pg] = order[cur]
+            cur += 1
+    table = table.to(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    ops.rope_cache_write(qkv, T, i32(seq), i32(pos), i32([0, 1]), inv, kc, vc, table, max_pages, page, H, K, hd, rot, False, True)
+    o = orig[:T].double().cpu().reshape(T, H + 2 * K, hd)
+    p_ = torch.tensor(pos)
+    want_q, want_k = o[:, :H].clone(), o[:, H:H + K].clone()
+    want_q[..., :rot] = plain_rope(o[:, :H, :rot], p_, inv.cpu(), "split_half")
+    want_k[..., :rot] = plain_rope(o[:, H:H + K, :rot], p_, inv.cpu(), "split_half")
+    got = qkv[:T].reshape(T, H + 2 * K, hd)
+    close(got[:, :H], want_q, 2e-2, 1e-2)
+    assert torch.equal(got[:, H:], orig[:T].reshape(T, H + 2 * K, hd)[:, H:]) and torch.equal(qkv[T], orig[T])
+    tbl = table.cpu()
+    pgs = torch.tensor([int(tbl[seq[t], pos[t] // page]) for t in range(T)])
+    rows = torch.tensor([pos[t] % page for t in range(T)])
+    close(kc.cpu()[pgs, rows], want_k, 2e-2, 1e-2)
+    assert torch.equal(vc.cpu()[pgs, rows].double(), o[:, H + K:])
+    mask = torch.ones(n_pages, page, dtype=torch.bool)
+    mask[pgs, rows] = False
+    assert bool((kc.cpu()[mask] == 0).all()) and bool((vc.cpu()[mask] == 0).all())
+
+
 def fill_cache(seq_lens, K, hd, page, dtype, seed=0, scatter=True):
     """Random keys/values for sequences, stored in shuffled pages. Returns dense and paged forms."""
     g = torch.Generator().manual_seed(seed)
