@@ -495,7 +495,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
 
     chain_release();
-    chain_wait();
+    // Positions, slots and page tables were written before this step's kernels began, and the keys
+    // and values of earlier positions before that: only the row of this step's own token (in the last
+    // tile) and the queries come from the kernel before this one.  So every warp whose first tile
+    // is not the last one asks for it before waiting for that kernel.
+    __syncthreads();                                     // the barriers exist
     const int seq = blockIdx.y;
     const int kvh = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
     const int token = p.seq_start[seq];
@@ -517,7 +521,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     };
     int blk = b0 + warp;
     if (*abort_flag != 0) blk = b1;
-    if (blk < b1 && lane == 0) { load_tile(&map_k, sK, kbar, blk); load_tile(&map_v, sV, vbar, blk); }
+    const bool early = blk < b1 && blk != blk_hi - 1;
+    if (early && lane == 0) { load_tile(&map_k, sK, kbar, blk); load_tile(&map_v, sV, vbar, blk); }
+    chain_wait();
+    if (!early && blk < b1 && lane == 0) { load_tile(&map_k, sK, kbar, blk); load_tile(&map_v, sV, vbar, blk); }
     // Q rows (heads of the group) -> shared, zero beyond G and beyond D
     for (int i = threadIdx.x; i < 16 * kChunks; i += NW * 32) {
         const int r = i / kChunks, c = i % kChunks;
