@@ -47,8 +47,9 @@ struct TcSmem {
     static constexpr int kA = kBM * kBK * 2;
     static constexpr int kB = BN * kBK * 2;
     static constexpr int kStage = kA * (MODE == kTcSwiGLU ? 2 : 1) + (kB < 1024 ? 1024 : kB);
-    // small token tiles leave room for two blocks per SM (decode: more blocks than SMs stay balanced)
-    static constexpr int kBudget = (BN <= 64 ? 110 : 200) * 1024;
+    // small token tiles leave room for two blocks per SM (decode: more blocks than SMs stay balanced);
+    // 64 tokens with two weight matrices would have two stages only, so they get the whole SM
+    static constexpr int kBudget = ((BN <= 32 || (BN == 64 && MODE != kTcSwiGLU)) ? 110 : 200) * 1024;
     static constexpr int kStages = (kBudget / kStage) < 8 ? (kBudget / kStage) : 8;
     static constexpr int kBytes = kStages * kStage + 1024 /*alignment*/ + 256 /*barriers*/;
     static constexpr int kTmemCols = (MODE == kTcSwiGLU ? 2 : 1) * BN < 32 ? 32 : (MODE == kTcSwiGLU ? 2 : 1) * BN;
@@ -743,10 +744,12 @@ int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_coun
     const int k_blocks = (K + kBK - 1) / kBK;
     const long tiles = (long)((n_features + kBM - 1) / kBM) * ((n_tokens + bn - 1) / bn);
     int splits = 1;
-    if (mode == kTcSwiGLU && bn <= 64 && tiles < sm_count && k_blocks >= 8) {
+    if (mode == kTcSwiGLU && bn <= 32 && tiles < sm_count && k_blocks >= 8) {
         // The SwiGLU ending needs complete sums, so its K split stays inside a cluster of two blocks
         // (measured at batch 8: 37.4 us against 41.8 us unsplit; larger clusters and cluster splits
-        // of the other products were slower than partial sums through global memory).
+        // of the other products were slower than partial sums through global memory).  With 64 tokens
+        // the partial sums are four times as large and one block per SM with a deep ring is faster
+        // (44.4 us against 48.4 us).
         *bn_out = bn; *splits_out = -2; return 0;
     }
     if (mode != kTcSwiGLU && tiles < sm_count) {
