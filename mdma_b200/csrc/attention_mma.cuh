@@ -783,8 +783,12 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
             return 0;
         };
         int rc;
-        if (splits == 1 && head_dim <= 64) rc = launch(attention_decode_tma_kernel<64, kDecodeKeys, 8>, 8, 64);
-        else if (splits == 1) rc = launch(attention_decode_tma_kernel<128, kDecodeKeys, 8>, 8, 128);
+        // few blocks: eight warps each (one block per SM); many: four warps and three blocks per SM
+        static int sm_count = 0;
+        if (sm_count == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
+        const bool wide = splits == 1 && (long)n_seqs * n_kv_heads < 2l * sm_count;
+        if (wide && head_dim <= 64) rc = launch(attention_decode_tma_kernel<64, kDecodeKeys, 8>, 8, 64);
+        else if (wide) rc = launch(attention_decode_tma_kernel<128, kDecodeKeys, 8>, 8, 128);
         else if (head_dim <= 64) rc = launch(attention_decode_tma_kernel<64, kDecodeKeys, 4>, 4, 64);
         else rc = launch(attention_decode_tma_kernel<128, kDecodeKeys, 4>, 4, 128);
         if (rc) return rc;
