@@ -221,7 +221,7 @@ def main() -> int:
         # stamps[i] is taken after every sequence's i-th token reached the host
         e2e_value = args.batch * args.steps / (stamps[-1] - stamps[-1 - args.steps])
         e2e = {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
-               "d2h_bytes_per_step": 8 * args.batch}
+               "d2h_bytes_per_step": 8 * sampler.max_rows}      # tokens and flags of every sampler row, one copy
 
     out = {
         "metric": "decode tokens/s (Llama-3.1-8B shape, batch 8, after 512-token prompts)",

@@ -82,7 +82,9 @@ class CacheGroup:
         last = (new_len - 1) // self.page_size
         if last >= self.max_pages:
             raise CacheFull(f"a sequence of {new_len} tokens needs more than {self.max_pages} pages")
-        missing = [p for p in range(first_needed, last + 1) if p not in have]
+        # the pages that cover [first_needed, old_len) are held already: look from the last of them on
+        start = max(first_needed, (old_len - 1) // self.page_size) if old_len > 0 else first_needed
+        missing = [p for p in range(start, last + 1) if p not in have]
         fresh = self.pages.acquire_many(len(missing))
         for p, page in zip(missing, fresh):
             have[p] = page
@@ -186,6 +188,8 @@ class SequenceCache:
                             f"beyond the context of {self.max_context}")
                 have = g.seq_pages.get(slot, {})
                 first = max(0, old + 1 - g.need.window) // self.page_size if g.need.window else 0
+                if old > 0:                    # pages up to the one that holds position old - 1 are held
+                    first = max(first, (old - 1) // self.page_size)
                 last = (old + n_new - 1) // self.page_size
                 want += sum(1 for p in range(first, last + 1) if p not in have)
             if want > g.pages.free_count:

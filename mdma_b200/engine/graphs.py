@@ -19,6 +19,7 @@ import torch
 
 from .. import ops
 from ..sampling.params import SamplingParams
+from ..cache.slots import CacheFull
 from .step import StepContext, StepError
 
 
@@ -35,7 +36,8 @@ class DecodeSession:
         self.arange = torch.arange(cap + 1, dtype=torch.int32, device=dev)
         self.logits = torch.empty((cap, engine.vocab_size), dtype=torch.float32, device=dev)
         self._host = torch.empty(3 * cap, dtype=torch.int32).pin_memory()
-        self._tok_host = torch.empty(2 * cap, dtype=torch.int32).pin_memory()
+        self._host_np = self._host.numpy()            # the same pinned words, written without a tensor in between
+        self._tok_host = torch.empty(2 * sampler.max_rows, dtype=torch.int32).pin_memory()
         self.ctx = StepContext(engine.rt, engine.workspace)
         self.steps_done: list[int] = []
         self.launches_per_step = 0          # kernels in one step (counted at the eager first run)
@@ -74,7 +76,7 @@ class DecodeSession:
         B = len(self.slots)
         if len(tokens) != B:
             raise StepError(f"{len(tokens)} tokens for {B} live sequences")
-        self._host[:B] = torch.as_tensor(list(tokens), dtype=torch.int32)
+        self._host_np[:B] = tokens
         self.ids[:B].copy_(self._host[:B], non_blocking=True)
 
     # ---- one step ----------------------------------------------------------
@@ -103,10 +105,10 @@ class DecodeSession:
         """Run one decode step for the live sequences; tokens stay on the device."""
         B = len(self.slots)
         ext = {s: 1 for s in self.slots}
-        why = self.engine.cache.can_extend(ext)
-        if why:
-            raise StepError(why)
-        self.engine.cache.extend(ext)
+        try:
+            self.engine.cache.extend(ext)
+        except CacheFull as e:
+            raise StepError(str(e)) from None
         p = self.params
         if p.temperature > 0.0 or (p.repetition_penalty != 1.0 and p.repetition_window > 0):
             self.sampler.stage_inputs(p, self.requests, self.steps_done, histories)
@@ -135,8 +137,7 @@ class DecodeSession:
 
     def read_tokens(self) -> tuple[list[int], list[int]]:
         """The tokens (and non-finite flags) the last step selected."""
-        B, cap = len(self.slots), self.engine.max_slots
-        self._tok_host[:B].copy_(self.sampler.tokens[:B], non_blocking=True)
-        self._tok_host[cap:cap + B].copy_(self.sampler.flags[:B], non_blocking=True)
+        B, cap = len(self.slots), self.sampler.max_rows
+        self._tok_host.copy_(self.sampler.tokens_and_flags.view(-1), non_blocking=True)     # one copy: 2 x rows integers
         torch.cuda.current_stream().synchronize()
         return self._tok_host[:B].tolist(), self._tok_host[cap:cap + B].tolist()

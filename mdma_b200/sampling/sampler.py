@@ -16,8 +16,9 @@ class DeviceSampler:
 
     def __init__(self, vocab_size: int, max_rows: int, device, history_cap: int = 64):
         self.vocab, self.max_rows, self.device = vocab_size, max_rows, device
-        self.tokens = torch.zeros(max_rows, dtype=torch.int32, device=device)
-        self.flags = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        # selected tokens and non-finite flags side by side, so that one copy brings both to the host
+        self.tokens_and_flags = torch.zeros(2, max_rows, dtype=torch.int32, device=device)
+        self.tokens, self.flags = self.tokens_and_flags[0], self.tokens_and_flags[1]
         self.uniforms = torch.zeros(max_rows, dtype=torch.float32, device=device)
         self.history_cap = max(1, history_cap)
         self.history = torch.zeros((max_rows, self.history_cap), dtype=torch.int32, device=device)
