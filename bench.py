@@ -2,6 +2,7 @@
 """Benchmark: decode tokens/s and prefill tokens/s at the Llama-3.1-8B shape.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --shape llama-2-7b | llama-3.2-1b [--batch B] [--prompt-len P] [--prefill-tokens T]
 
 Prints ONE JSON line.  The default run has the layer sizes of the
 Llama-3.1-8B shape with random bfloat16 weights, a batch of 8 sequences
@@ -32,7 +33,19 @@ LLAMA_31_8B = dict(
     rope_theta=500000.0, rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
                                            high_freq_factor=4.0, original_max_position_embeddings=8192),
     rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=131072)
-FULL_LAYERS = 32
+# The other shapes that the baseline names (same architecture, other sizes): `--shape` picks one.
+LLAMA_2_7B = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=32, hidden_size=4096,
+    num_attention_heads=32, num_key_value_heads=32, head_dim=128, intermediate_size=11008, vocab_size=32000,
+    rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=4096)
+LLAMA_32_1B = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=16, hidden_size=2048,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192, vocab_size=128256,
+    rope_theta=500000.0, rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0,
+                                           high_freq_factor=4.0, original_max_position_embeddings=8192),
+    rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072)
+SHAPES = {"llama-3.1-8b": ("Llama-3.1-8B shape", LLAMA_31_8B), "llama-2-7b": ("Llama-2-7B shape", LLAMA_2_7B),
+          "llama-3.2-1b": ("Llama-3.2-1B shape", LLAMA_32_1B)}
 
 
 def peaks():
@@ -119,7 +132,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--prompt-len", type=int, default=512)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the shape has (named in config)")
+    ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES), help="layer sizes (default: the headline shape)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in config)")
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement (profiling runs)")
     ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill (profiling runs)")
@@ -142,11 +157,16 @@ def main() -> int:
     from mdma_b200.sampling import SamplingParams
     from mdma_b200.sampling.sampler import DeviceSampler
 
-    cfg = dict(LLAMA_31_8B, num_hidden_layers=args.layers)
+    shape_name, shape_cfg = SHAPES[args.shape]
+    FULL_LAYERS = shape_cfg["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = FULL_LAYERS
+    cfg = dict(shape_cfg, num_hidden_layers=args.layers)
     hbm_gbs, bf16_tflops, peak_src = peaks()
     torch.cuda.set_device(0)
     max_batch = max(args.batch, 1 if args.no_points else 64)
-    eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_batch=max_batch, max_context=args.context)
+    eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_batch=max_batch,
+                 max_context=max(args.context, args.prefill_tokens))
     sampler = DeviceSampler(eng.vocab_size, eng.max_slots, eng.device)
     gen = torch.Generator().manual_seed(0)
 
@@ -178,7 +198,7 @@ def main() -> int:
             eng.release(s)
         return ms / steps, per_graph * steps, ctx_now
 
-    def time_prefill(T=2048):
+    def time_prefill(T=args.prefill_tokens):
         times = []
         for i in range(warmup + 5):
             s = eng.acquire()
@@ -224,18 +244,19 @@ def main() -> int:
                "d2h_bytes_per_step": 8 * sampler.max_rows}      # tokens and flags of every sampler row, one copy
 
     out = {
-        "metric": "decode tokens/s (Llama-3.1-8B shape, batch 8, after 512-token prompts)",
+        "metric": f"decode tokens/s ({shape_name}, batch {args.batch}, after {args.prompt_len}-token prompts)",
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (uniform random token ids, random N(0,0.02) weights)",
         "impl": "ours",
-        "config": {"model": "Llama-3.1-8B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
+        "config": {"model": shape_name, "layers": args.layers, "layers_full": FULL_LAYERS,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "global_batch": args.batch, "seq_len": args.context, "prompt_len": args.prompt_len,
                    "context_at_end": ctx_end, "parallelism": "single GPU", "page_size": eng.page_size,
-                   "cuda_graph": True, "l2": "inputs (15 GB of weights per step) larger than L2, no flush",
+                   "cuda_graph": True,
+                   "l2": f"inputs ({bytes_step / 1e9:.1f} GB of weights and cache per step) larger than L2, no flush",
                    "peaks": peak_src},
         "e2e": e2e, "gpu_launches": launches, "clocks": None,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
