@@ -80,6 +80,25 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
 }
+// Reads of another block's shared memory (`remote` from cluster_map).
+__device__ __forceinline__ float cluster_load_f32(uint32_t remote) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t cluster_load_u32(uint32_t remote) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long cluster_load_u64(uint32_t remote) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ void cluster_store_u64(uint32_t remote, unsigned long long v) {
+    asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(remote), "l"(v) : "memory");
+}
 __device__ __forceinline__ void cluster_store_f32(uint32_t remote, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }

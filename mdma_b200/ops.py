@@ -161,22 +161,29 @@ def argmax(logits: torch.Tensor, tokens: torch.Tensor, flags: Optional[torch.Ten
           _ptr(scratch), ctypes.c_long(scratch.numel()), _stream(), launches=2)
 
 
+def sample_scratch_words(n_rows: int, vocab: int) -> int:
+    """Floats of scratch `sample` needs: exponentials, candidate probabilities and candidate ids of every row."""
+    return 3 * n_rows * vocab
+
+
 def sample(logits: torch.Tensor, uniforms: torch.Tensor, tokens: torch.Tensor, probs_scratch: torch.Tensor,
            temperature: float, top_p: float, min_p: float, penalty: float, penalty_window: int,
            history: Optional[torch.Tensor] = None, history_len: Optional[torch.Tensor] = None,
-           flags: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
+           flags: Optional[torch.Tensor] = None, n_rows: Optional[int] = None, impl: int = 0) -> None:
+    """`impl`: 0 picks (a cluster of eight blocks per row when the row fits), 1 one block per row, 2 the cluster."""
     _need_cuda(logits, uniforms, tokens, probs_scratch, history, history_len, flags)
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     assert uniforms.dtype == torch.float32 and tokens.dtype == torch.int32
     n = logits.shape[0] if n_rows is None else n_rows
-    assert probs_scratch.dtype == torch.float32 and probs_scratch.numel() >= n * logits.shape[1]
+    assert probs_scratch.dtype == torch.float32 and probs_scratch.numel() >= sample_scratch_words(n, logits.shape[1])
     hstride = 0
     if history is not None:
         assert history.dtype == torch.int32 and history_len.dtype == torch.int32 and history.is_contiguous()
         hstride = history.shape[1]
     _call("core", "mdma_sample", _ptr(logits), _i(n), _i(logits.shape[1]), _ptr(history),
           _ptr(history_len), _i(hstride), _ptr(uniforms), _f(temperature), _f(top_p), _f(min_p),
-          _f(penalty), _i(penalty_window), _ptr(probs_scratch), _ptr(tokens), _ptr(flags), _stream())
+          _f(penalty), _i(penalty_window), _ptr(probs_scratch), ctypes.c_long(probs_scratch.numel()), _ptr(tokens),
+          _ptr(flags), _i(impl), _stream())
 
 
 def advance_decode(tokens: torch.Tensor, ids: torch.Tensor, tok_pos: torch.Tensor, seq_pos0: torch.Tensor,

@@ -28,7 +28,8 @@ class DeviceSampler:
 
     def ensure_probs(self) -> None:
         if self._probs is None:
-            self._probs = torch.empty(self.max_rows * self.vocab, dtype=torch.float32, device=self.device)
+            self._probs = torch.empty(ops.sample_scratch_words(self.max_rows, self.vocab), dtype=torch.float32,
+                                      device=self.device)
 
     def stage_inputs(self, params: SamplingParams, requests, steps, histories=None) -> bool:
         """Upload what the sampled path reads: one uniform number per row, keyed by

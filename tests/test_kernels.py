@@ -524,17 +524,18 @@ def test_argmax_lowest_index_and_flags():
     assert flags[:5].tolist() == [0, 0, 1, 1, 0]
 
 
-@pytest.mark.parametrize("vocab", [331, 5000])
+@pytest.mark.parametrize("impl", [1, 2])          # one block per row; a cluster of eight blocks per row
+@pytest.mark.parametrize("vocab", [331, 5000, 40003])
 @pytest.mark.parametrize("opts", [dict(temperature=0.8, top_p=0.95, min_p=0.05, repetition_penalty=1.1),
                                   dict(temperature=1.3, top_p=1.0, min_p=0.0, repetition_penalty=1.0),
                                   dict(temperature=0.5, top_p=0.3, min_p=0.0, repetition_penalty=1.0),
                                   dict(temperature=1.0, top_p=1.0, min_p=0.2, repetition_penalty=1.5),
                                   dict(temperature=0.0, top_p=1.0, min_p=0.0, repetition_penalty=1.7)])
-def test_sample_matches_the_host_sampler(vocab, opts):
+def test_sample_matches_the_host_sampler(vocab, opts, impl):
     """Same uniform number, same token as the plain sampler (src/sampler.rs:34-135)."""
     ops = ops_mod()
     torch.manual_seed(vocab)
-    n = 24
+    n = 24 if vocab < 20000 else 5
     logits = torch.randn(n, vocab) * 3
     logits[3, 10] = logits[3, 20] = logits[3].max() + 1           # tied leaders
     hist = torch.randint(0, vocab, (n, 64), dtype=torch.int32)
@@ -543,9 +544,9 @@ def test_sample_matches_the_host_sampler(vocab, opts):
     u = torch.rand(n)
     tok = torch.zeros(n, dtype=torch.int32, device=DEV)
     flags = torch.zeros(n, dtype=torch.int32, device=DEV)
-    scratch = torch.empty(n * vocab, device=DEV)
+    scratch = torch.empty(ops.sample_scratch_words(n, vocab), device=DEV)
     ops.sample(logits.to(DEV), u.to(DEV), tok, scratch, opts["temperature"], opts["top_p"], opts["min_p"],
-               opts["repetition_penalty"], 64, hist.to(DEV), hlen.to(DEV), flags)
+               opts["repetition_penalty"], 64, hist.to(DEV), hlen.to(DEV), flags, impl=impl)
     want = [plain_sample(logits[i].tolist(), hist[i].tolist(), float(u[i]), opts["temperature"], opts["top_p"],
                          opts["min_p"], opts["repetition_penalty"], 64) for i in range(n)]
     got = tok.tolist()
@@ -554,15 +555,16 @@ def test_sample_matches_the_host_sampler(vocab, opts):
     assert flags.sum().item() == 0
 
 
-def test_sample_follows_the_distribution():
+@pytest.mark.parametrize("impl", [1, 2])
+def test_sample_follows_the_distribution(impl):
     ops = ops_mod()
     vocab, n = 50, 4000
     row = torch.randn(vocab) * 2
     logits = row.repeat(n, 1).to(DEV)
     u = torch.rand(n, generator=torch.Generator().manual_seed(0)).to(DEV)
     tok = torch.zeros(n, dtype=torch.int32, device=DEV)
-    scratch = torch.empty(n * vocab, device=DEV)
-    ops.sample(logits, u, tok, scratch, 1.0, 1.0, 0.0, 1.0, 0)
+    scratch = torch.empty(ops.sample_scratch_words(n, vocab), device=DEV)
+    ops.sample(logits, u, tok, scratch, 1.0, 1.0, 0.0, 1.0, 0, impl=impl)
     freq = torch.bincount(tok.long().cpu(), minlength=vocab).double() / n
     p = torch.softmax(row.double(), 0)
     assert (freq - p).abs().max() < 4 * (p.max() * (1 - p.max()) / n) ** 0.5 + 0.01
