@@ -689,24 +689,25 @@ static int run_tc2(const void* x, int ldx, const void* w, const void* w2, int K,
     const int pairs = (int)(tiles < sm_count / 2 ? tiles : sm_count / 2);
     cfg.gridDim = dim3(pairs * 2, 1, 1);
     cfg.blockDim = dim3(kTc2Threads); cfg.dynamicSmemBytes = S::kBytes; cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeCooperative;       // pairs wait on one another: all must be resident
-    attr[1].val.cooperative = 1;
     cfg.attrs = attr;
+    cfg.numAttrs = 1;
     // The even split of K blocks pays when the tiles do not fill whole rounds of pairs, and only with
     // two weight matrices: with one, the product runs at the power limit of the device either way
     // (measured: 2048 tokens, gate+up 455 -> 425 us; QKV 79 -> 83 us, down 180 -> 192 us).
-    const bool uneven = MODE == kTcSwiGLU && tiles > pairs && tiles % pairs != 0;
-    if (uneven && p.sk_partial != nullptr && p.sk_flags != nullptr) {
-        cfg.numAttrs = 2;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mw2, mx, p);
-        if (e == cudaSuccess) return 0;
-        (void)cudaGetLastError();          // the device cannot hold all pairs at once: whole tiles per pair instead
+    // A pair that finishes a shared tile waits for the pair before it (a lower block index, so it has
+    // been started no later), with a limit.  The split is only used when the device can hold all pairs
+    // at once (asked once); the launch is an ordinary cluster launch, which profilers take.
+    static int max_pairs = -1;
+    if (max_pairs < 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<MODE>, &cfg) != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+        max_pairs = n;
     }
-    p.sk_partial = nullptr; p.sk_flags = nullptr;
-    cfg.numAttrs = 1;
+    const bool uneven = MODE == kTcSwiGLU && tiles > pairs && tiles % pairs != 0;
+    if (!(uneven && pairs <= max_pairs)) { p.sk_partial = nullptr; p.sk_flags = nullptr; }
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mw2, mx, p);
     if (e != cudaSuccess) return fail("gemm_tc2: launch failed: %s", cudaGetErrorString(e));
     return 0;

@@ -15,7 +15,7 @@
 namespace mdma {
 
 constexpr int kSampleThreads = 1024;
-constexpr int kWarpHistBytes = (kSampleThreads / 32) * 256 * 8;     // a histogram of 256 digits per warp
+constexpr int kWarpHistBytes = (kSampleThreads / 32) * 256 * 3 * 4;     // a histogram of 256 digits (three limbs) per warp
 
 struct ArgMax { float v; int i; };
 __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
@@ -135,19 +135,39 @@ __device__ __forceinline__ void for_each(const float* __restrict__ v, int n, F f
     }
 }
 
-// Adds `mass` to bin `digit` of a histogram that belongs to the calling warp alone.  All 32 lanes call
-// it together; lanes that hold the same digit are summed by the warp first (match + two 20-bit
-// reductions: a mass is at most 2^40), and one of them adds the sum with a plain store.  A 64-bit
-// shared-memory add that many threads aim at one word costs about 75 cycles each, and most elements of a
-// pass share a few digits.
-__device__ __forceinline__ void warp_hist_add(unsigned long long* warp_hist, bool active, int digit,
-                                              unsigned long long mass) {
-    const unsigned peers = __match_any_sync(0xffffffffu, active ? digit : -1);
-    const unsigned lo = __reduce_add_sync(peers, (unsigned)(mass & 0xFFFFFull));
-    const unsigned hi = __reduce_add_sync(peers, (unsigned)(mass >> 20));
-    if (active && (int)(threadIdx.x & 31) == __ffs(peers) - 1) warp_hist[digit] += ((unsigned long long)hi << 20) + lo;
-    __syncwarp();
+// A histogram of masses over the 256 digits of a pass, one per warp, kept as three 32-bit limbs per
+// digit (14 + 14 + the rest of a mass) so that it takes the native 32-bit shared-memory add: a 64-bit
+// add that many threads aim at one word costs about 75 cycles each.  A warp adds at most 4096 masses of
+// at most 2^47, so no limb overflows.
+constexpr int kLimbWords = 256 * 3;
+__device__ __forceinline__ void limb_add(unsigned* warp_hist, int digit, unsigned long long mass) {
+    atomicAdd(&warp_hist[digit * 3], (unsigned)(mass & 0x3FFFull));
+    atomicAdd(&warp_hist[digit * 3 + 1], (unsigned)((mass >> 14) & 0x3FFFull));
+    atomicAdd(&warp_hist[digit * 3 + 2], (unsigned)(mass >> 28));
 }
+__device__ __forceinline__ unsigned long long limb_value(const unsigned* warp_hist, int digit) {
+    return (unsigned long long)warp_hist[digit * 3] + ((unsigned long long)warp_hist[digit * 3 + 1] << 14) +
+           ((unsigned long long)warp_hist[digit * 3 + 2] << 28);
+}
+
+// A thread's own two digits of a pass: most of a thread's elements share one or two digits, so they are
+// summed in registers and reach the warp's histogram at the end of the pass; an element with a third
+// digit goes there at once.
+struct DigitPair {
+    int d0 = -1, d1 = -1;
+    unsigned long long m0 = 0ull, m1 = 0ull;
+    __device__ __forceinline__ void add(unsigned* warp_hist, int digit, unsigned long long mass) {
+        if (digit == d0) m0 += mass;
+        else if (digit == d1) m1 += mass;
+        else if (d0 < 0) { d0 = digit; m0 = mass; }
+        else if (d1 < 0) { d1 = digit; m1 = mass; }
+        else limb_add(warp_hist, digit, mass);
+    }
+    __device__ __forceinline__ void flush(unsigned* warp_hist) {
+        if (d0 >= 0) limb_add(warp_hist, d0, m0);
+        if (d1 >= 0) limb_add(warp_hist, d1, m1);
+    }
+};
 
 // The sum of a 64-bit value over the block (order-free), through `slot`.
 __device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long* slot) {
@@ -213,6 +233,45 @@ __device__ __forceinline__ void pick_digit(const unsigned long long* bins, unsig
     digit = misc[0];
     new_above = *out_above;
     __syncthreads();
+}
+
+// What a row's draw depends on besides its logits.  The uniform number is either given (`uniforms`) or
+// made here from (seed, request, step) with the generator of the host side (three rounds of splitmix64,
+// 24 bits).  The history is a ring of `history_stride` recent token ids per row with the count of
+// tokens ever added; the repetition penalty looks at the last `penalty_window` of them (the order does
+// not matter: a token is divided or multiplied once per occurrence).  With `advance` the kernel
+// appends the token it selected to the ring and moves the row's step counter on, so that a decode loop
+// replayed as a graph needs nothing from the host between steps.
+struct SampleState {
+    int* history; int* history_len; int history_stride;
+    const float* uniforms;
+    const int* requests; int* steps; unsigned long long seed;
+    int advance;
+};
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__device__ __forceinline__ float row_uniform(const SampleState& st, int r) {
+    if (st.uniforms != nullptr) return st.uniforms[r];
+    const unsigned long long z = mix64(mix64(mix64(st.seed) ^ (unsigned long long)st.requests[r]) ^ (unsigned long long)st.steps[r]);
+    return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+// One thread: the row's result, and what the next step of the row starts from.
+__device__ __forceinline__ void finish_row(const SampleState& st, int r, int token, int flag, int* tokens, int* flags) {
+    tokens[r] = token;
+    if (flags) flags[r] = flag;
+    if (st.advance) {
+        if (st.steps) st.steps[r] += 1;
+        if (st.history) {
+            const int c = st.history_len[r];
+            st.history[(size_t)r * st.history_stride + (c % st.history_stride)] = token;
+            st.history_len[r] = c + 1;
+        }
+    }
 }
 
 // ---- few candidates: sort them ------------------------------------------------------
@@ -283,7 +342,7 @@ struct Crossing { int pos; unsigned bits; unsigned long long mass; };
 __device__ Crossing find_crossing(const float* __restrict__ probs, int n, unsigned long long target,
                                   unsigned limit_bits, int limit_pos,
                                   unsigned long long* hist /*256*/, int* misc /*8*/, int* warp_counts /*32*/,
-                                  unsigned long long* warp_hists /*warps x 256*/) {
+                                  unsigned* warp_hists /*warps x 256 x 3 limbs*/) {
     auto takes_part = [&](int i, float p) -> bool {
         if (!(p > 0.f)) return false;
         if (limit_pos < 0) return true;
@@ -291,23 +350,23 @@ __device__ Crossing find_crossing(const float* __restrict__ probs, int n, unsign
         return bits > limit_bits || (bits == limit_bits && i <= limit_pos);
     };
     const int warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    unsigned long long* my_hist = warp_hists + warp * 256;
+    unsigned* my_hist = warp_hists + warp * kLimbWords;
     unsigned prefix = 0, prefix_mask = 0;
     unsigned long long above = 0;     // mass of elements with bit pattern above the current prefix range
     for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int b = threadIdx.x & 31; b < 256; b += 32) my_hist[b] = 0ull;
+        for (int b = threadIdx.x & 31; b < kLimbWords; b += 32) my_hist[b] = 0u;
         __syncwarp();
-        for (int base = 0; base < n; base += blockDim.x) {
-            const int i = base + threadIdx.x;
-            const float p = i < n ? probs[i] : 0.f;
+        DigitPair own;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float p = probs[i];
             const unsigned bits = __float_as_uint(p);
-            const bool active = i < n && (bits & prefix_mask) == prefix && takes_part(i, p);
-            warp_hist_add(my_hist, active, (int)((bits >> shift) & 255u), active ? mass_of(p) : 0ull);
+            if ((bits & prefix_mask) == prefix && takes_part(i, p)) own.add(my_hist, (int)((bits >> shift) & 255u), mass_of(p));
         }
+        own.flush(my_hist);
         __syncthreads();
         for (int b = threadIdx.x; b < 256; b += blockDim.x) {
             unsigned long long t = 0ull;
-            for (int w = 0; w < n_warps; ++w) t += warp_hists[w * 256 + b];
+            for (int w = 0; w < n_warps; ++w) t += limb_value(warp_hists + w * kLimbWords, b);
             hist[b] = t;
         }
         __syncthreads();
@@ -376,8 +435,7 @@ __device__ Crossing find_crossing(const float* __restrict__ probs, int n, unsign
 // vocabulary.  `scratch` holds three words per vocabulary entry and row: exponentials, the candidates'
 // probabilities, their token ids.
 __global__ void __launch_bounds__(kSampleThreads)
-sample_kernel(const float* __restrict__ logits, int vocab, const int* __restrict__ history,
-              const int* __restrict__ history_len, int history_stride, const float* __restrict__ uniforms,
+sample_kernel(const float* __restrict__ logits, int vocab, const SampleState st,
               float temperature, float top_p, float min_p, float penalty, int penalty_window,
               float* __restrict__ scratch, int* __restrict__ tokens, int* __restrict__ flags) {
     __shared__ float fscratch[32];
@@ -386,7 +444,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const int* __restrict
     __shared__ __align__(8) int misc[8];
     __shared__ int warp_counts[32];
     __shared__ int bad;
-    extern __shared__ __align__(16) unsigned long long warp_hists[];      // one histogram of 256 digits per warp
+    extern __shared__ __align__(16) unsigned warp_hists[];      // one histogram of 256 digits per warp
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * vocab;
     float* probs = scratch + (size_t)r * 3 * vocab;
@@ -407,13 +465,14 @@ sample_kernel(const float* __restrict__ logits, int vocab, const int* __restrict
     __syncthreads();
     // 2. repetition penalty on the last `penalty_window` tokens of the history; a
     //    token that occurs several times is penalised once per occurrence, in order
-    const bool penalised = penalty != 1.0f && history != nullptr && penalty_window > 0;
+    const bool penalised = penalty != 1.0f && st.history != nullptr && penalty_window > 0;
     if (penalised) {
         if (threadIdx.x == 0) {
-            const int n = history_len[r];
-            const int* hrow = history + (size_t)r * history_stride;
-            for (int j = max(0, n - penalty_window); j < n; ++j) {
-                const int id = hrow[j];
+            const int count = st.history_len[r];
+            const int m = min(min(penalty_window, count), st.history_stride);
+            const int* hrow = st.history + (size_t)r * st.history_stride;
+            for (int e = 0; e < m; ++e) {
+                const int id = hrow[(count - m + e) % st.history_stride];
                 if (id >= 0 && id < vocab) {
                     const float l = probs[id];
                     probs[id] = l > 0.f ? l / penalty : l * penalty;
@@ -427,7 +486,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const int* __restrict
     // 3. greedy when temperature <= 0
     a = block_argmax(a, ascratch);
     if (temperature <= 0.f || bad) {
-        if (threadIdx.x == 0) { tokens[r] = a.i == 0x7fffffff ? 0 : a.i; if (flags) flags[r] = bad; }
+        if (threadIdx.x == 0) finish_row(st, r, a.i == 0x7fffffff ? 0 : a.i, bad, tokens, flags);
         return;
     }
     // 4. softmax of logits / temperature: the leader's exponential is exactly 1
@@ -477,16 +536,16 @@ sample_kernel(const float* __restrict__ logits, int vocab, const int* __restrict
     __syncthreads();
     const int n_cand = misc[4];
     if (n_cand == 0) {                                      // cannot happen with finite logits; keep the leader
-        if (threadIdx.x == 0) { tokens[r] = a.i; if (flags) flags[r] = 0; }
+        if (threadIdx.x == 0) finish_row(st, r, a.i, 0, tokens, flags);
         return;
     }
     if (n_cand <= kSmallMax) {
         // few candidates: sort them (the warps' histograms are not needed: their room holds the keys)
-        unsigned long long* keys = warp_hists;
-        unsigned long long* cum = warp_hists + kSmallMax;
+        unsigned long long* keys = reinterpret_cast<unsigned long long*>(warp_hists);
+        unsigned long long* cum = keys + kSmallMax;
         keys[threadIdx.x] = (int)threadIdx.x < n_cand ? small_key(cand_p[threadIdx.x], cand_id[threadIdx.x]) : 0ull;
-        const int id = small_select(keys, cum, n_cand, top_p, uniforms[r], a.i, misc, hist);
-        if (threadIdx.x == 0) { tokens[r] = id; if (flags) flags[r] = 0; }
+        const int id = small_select(keys, cum, n_cand, top_p, row_uniform(st, r), a.i, misc, hist);
+        if (threadIdx.x == 0) finish_row(st, r, id, 0, tokens, flags);
         return;
     }
     // 6. top-p: the smallest descending prefix whose mass reaches top_p
@@ -502,11 +561,11 @@ sample_kernel(const float* __restrict__ logits, int vocab, const int* __restrict
         kept = block_sum_u64(mine, &hist[0]);
     }
     // 7. draw: first element of the descending order whose running mass reaches u * kept
-    const float u = uniforms[r];
+    const float u = row_uniform(st, r);
     unsigned long long target = (unsigned long long)((double)u * (double)kept);
     if (target < 1ull) target = 1ull;
     const Crossing drawn = find_crossing(cand_p, n_cand, target, limit_bits, limit_pos, hist, misc, warp_counts, warp_hists);
-    if (threadIdx.x == 0) { tokens[r] = drawn.pos >= 0 ? cand_id[drawn.pos] : a.i; if (flags) flags[r] = 0; }
+    if (threadIdx.x == 0) finish_row(st, r, drawn.pos >= 0 ? cand_id[drawn.pos] : a.i, 0, tokens, flags);
 }
 
 // ---- the same for a cluster of eight blocks per row ---------------------------------
@@ -531,7 +590,7 @@ struct ClusterCrossing { int index; unsigned bits; unsigned long long mass; };
 __device__ ClusterCrossing find_crossing_cluster(const float* slice, int n, int lo, unsigned long long target,
                                                  unsigned limit_bits, int limit_index, int fallback_index,
                                                  SampleExchange* xch, unsigned long long* total /*256*/, int* misc,
-                                                 int* warp_counts, int& turn, unsigned long long* warp_hists) {
+                                                 int* warp_counts, int& turn, unsigned* warp_hists) {
     const uint32_t xch_addr = ptx::smem_addr(xch);
     const int rank = (int)ptx::cluster_rank();
     auto takes_part = [&](int gi, float p) -> bool {
@@ -541,24 +600,24 @@ __device__ ClusterCrossing find_crossing_cluster(const float* slice, int n, int 
         return bits > limit_bits || (bits == limit_bits && gi <= limit_index);
     };
     const int warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    unsigned long long* my_hist = warp_hists + warp * 256;
+    unsigned* my_hist = warp_hists + warp * kLimbWords;
     unsigned prefix = 0, prefix_mask = 0;
     unsigned long long above = 0;
     for (int shift = 24; shift >= 0; shift -= 8) {
         unsigned long long* hist = xch->hist[turn & 1];
-        for (int b = threadIdx.x & 31; b < 256; b += 32) my_hist[b] = 0ull;
+        for (int b = threadIdx.x & 31; b < kLimbWords; b += 32) my_hist[b] = 0u;
         __syncwarp();
-        for (int base = 0; base < n; base += blockDim.x) {
-            const int i = base + threadIdx.x;
-            const float p = i < n ? slice[i] : 0.f;
+        DigitPair own;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float p = slice[i];
             const unsigned bits = __float_as_uint(p);
-            const bool active = i < n && (bits & prefix_mask) == prefix && takes_part(lo + i, p);
-            warp_hist_add(my_hist, active, (int)((bits >> shift) & 255u), active ? mass_of(p) : 0ull);
+            if ((bits & prefix_mask) == prefix && takes_part(lo + i, p)) own.add(my_hist, (int)((bits >> shift) & 255u), mass_of(p));
         }
+        own.flush(my_hist);
         __syncthreads();
         for (int b = threadIdx.x; b < 256; b += blockDim.x) {
             unsigned long long t = 0ull;
-            for (int w = 0; w < n_warps; ++w) t += warp_hists[w * 256 + b];
+            for (int w = 0; w < n_warps; ++w) t += limb_value(warp_hists + w * kLimbWords, b);
             hist[b] = t;
         }
         ptx::cluster_sync();
@@ -649,12 +708,12 @@ __device__ ClusterCrossing find_crossing_cluster(const float* slice, int n, int 
 }
 
 __global__ void __launch_bounds__(kSampleThreads)
-sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, const int* __restrict__ history,
-                      const int* __restrict__ history_len, int history_stride, const float* __restrict__ uniforms,
+sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, const SampleState st,
                       float temperature, float top_p, float min_p, float penalty, int penalty_window,
                       int* __restrict__ tokens, int* __restrict__ flags) {
     extern __shared__ __align__(16) float slice[];          // `per` floats, then the warps' histograms
-    unsigned long long* warp_hists = reinterpret_cast<unsigned long long*>(slice + per);
+    unsigned* warp_hists = reinterpret_cast<unsigned*>(slice + per);
+    unsigned long long* small_keys = reinterpret_cast<unsigned long long*>(warp_hists);
     __shared__ SampleExchange xch;
     __shared__ int window[64];
     __shared__ unsigned long long total[256];
@@ -680,13 +739,13 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
     if (nonfinite) bad = 1;
     __syncthreads();
     // 2. repetition penalty: every block walks the window and changes the tokens it holds, in order
-    if (penalty != 1.0f && history != nullptr && penalty_window > 0) {
-        const int hn = history_len[r];
-        const int* hrow = history + (size_t)r * history_stride;
-        const int first = max(0, hn - penalty_window);
-        for (int base = first; base < hn; base += 64) {          // 64 ids at a time through shared memory
-            const int m = min(64, hn - base);
-            if ((int)threadIdx.x < m) window[threadIdx.x] = hrow[base + threadIdx.x];
+    if (penalty != 1.0f && st.history != nullptr && penalty_window > 0) {
+        const int count = st.history_len[r];
+        const int m_all = min(min(penalty_window, count), st.history_stride);
+        const int* hrow = st.history + (size_t)r * st.history_stride;
+        for (int base = 0; base < m_all; base += 64) {           // 64 ids at a time through shared memory
+            const int m = min(64, m_all - base);
+            if ((int)threadIdx.x < m) window[threadIdx.x] = hrow[(count - m_all + base + (int)threadIdx.x) % st.history_stride];
             __syncthreads();
             if (threadIdx.x == 0) {
                 for (int j = 0; j < m; ++j) {
@@ -726,7 +785,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
     const int any_bad = misc[5];
     __syncthreads();
     if (temperature <= 0.f || any_bad) {
-        if (rank == 0 && threadIdx.x == 0) { tokens[r] = a.i == 0x7fffffff ? 0 : a.i; if (flags) flags[r] = any_bad; }
+        if (rank == 0 && threadIdx.x == 0) finish_row(st, r, a.i == 0x7fffffff ? 0 : a.i, any_bad, tokens, flags);
         ptx::cluster_sync();          // nobody leaves while its words may still be read
         return;
     }
@@ -780,8 +839,8 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
     if (cand_all <= kSmallMax) {
         // few candidates: every block sends its own to the first block, which sorts them
         // (their order of arrival does not matter); the keys live where the warps' histograms would
-        const uint32_t keys0 = ptx::cluster_map(ptx::smem_addr(warp_hists), 0);
-        if (rank == 0) for (int i = threadIdx.x; i < 2 * kSmallMax; i += blockDim.x) warp_hists[i] = 0ull;
+        const uint32_t keys0 = ptx::cluster_map(ptx::smem_addr(small_keys), 0);
+        if (rank == 0) for (int i = threadIdx.x; i < 2 * kSmallMax; i += blockDim.x) small_keys[i] = 0ull;
         if (threadIdx.x == 0) misc[2] = 0;
         ptx::cluster_sync();                         // the first block's list is cleared
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -793,8 +852,8 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
         }
         ptx::cluster_sync();                         // the list is complete
         if (rank == 0) {
-            const int id = small_select(warp_hists, warp_hists + kSmallMax, cand_all, top_p, uniforms[r], a.i, misc, total);
-            if (threadIdx.x == 0) { tokens[r] = id; if (flags) flags[r] = 0; }
+            const int id = small_select(small_keys, small_keys + kSmallMax, cand_all, top_p, row_uniform(st, r), a.i, misc, total);
+            if (threadIdx.x == 0) finish_row(st, r, id, 0, tokens, flags);
         }
         return;
     }
@@ -819,12 +878,12 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
         limit_index = cut.index;
     }
     // 7. draw: first element of the descending order whose running mass reaches u * kept
-    const float u = uniforms[r];
+    const float u = row_uniform(st, r);
     unsigned long long target = (unsigned long long)((double)u * (double)kept);
     if (target < 1ull) target = 1ull;
     const ClusterCrossing drawn = find_crossing_cluster(slice, n, lo, target, limit_bits, limit_index, a.i, &xch, total,
                                                         misc, warp_counts, turn, warp_hists);
-    if (rank == 0 && threadIdx.x == 0) { tokens[r] = drawn.index >= 0 ? drawn.index : a.i; if (flags) flags[r] = 0; }
+    if (rank == 0 && threadIdx.x == 0) finish_row(st, r, drawn.index >= 0 ? drawn.index : a.i, 0, tokens, flags);
 }
 
 }  // namespace mdma
@@ -856,12 +915,22 @@ extern "C" int mdma_argmax(const float* logits, int n_rows, int vocab, int* toke
 // Floats (4-byte words) of scratch mdma_sample needs: three per vocabulary entry of every row.
 extern "C" long mdma_sample_scratch(int n_rows, int vocab) { return 3l * n_rows * vocab; }
 
-extern "C" int mdma_sample(const float* logits, int n_rows, int vocab, const int* history,
-                           const int* history_len, int history_stride, const float* uniforms,
+// Either `uniforms` (one number per row) or `requests`, `steps` and `seed` (the numbers are then made on
+// the device); `advance`: append the selected tokens to the history rings and add one to the steps.
+extern "C" int mdma_sample(const float* logits, int n_rows, int vocab, int* history,
+                           int* history_len, int history_stride, const float* uniforms,
+                           const int* requests, int* steps, unsigned long long seed, int advance,
                            float temperature, float top_p, float min_p, float penalty, int penalty_window,
                            float* probs_scratch, long scratch_words, int* tokens, int* flags, int impl, cudaStream_t stream) {
     MDMA_REQUIRE(vocab > 0 && n_rows >= 0, "sample: bad sizes");
-    MDMA_REQUIRE(probs_scratch != nullptr && uniforms != nullptr, "sample: scratch and uniform numbers are required");
+    MDMA_REQUIRE(probs_scratch != nullptr, "sample: scratch is required");
+    MDMA_REQUIRE(uniforms != nullptr || (requests != nullptr && steps != nullptr),
+                 "sample: uniform numbers, or requests and steps to make them from, are required");
+    MDMA_REQUIRE(history == nullptr || (history_len != nullptr && history_stride > 0), "sample: a history needs its lengths and a row length");
+    MDMA_REQUIRE(penalty > 0.f, "sample: repetition penalty must be positive");
+    SampleState st;
+    st.history = history; st.history_len = history_len; st.history_stride = history_stride;
+    st.uniforms = uniforms; st.requests = requests; st.steps = steps; st.seed = seed; st.advance = advance;
     MDMA_REQUIRE(scratch_words >= 3l * n_rows * vocab, "sample: %ld words of scratch needed, %ld given", 3l * n_rows * vocab, scratch_words);
     MDMA_REQUIRE(penalty > 0.f, "sample: repetition penalty must be positive");
     if (n_rows == 0) return 0;
@@ -885,9 +954,8 @@ extern "C" int mdma_sample(const float* logits, int n_rows, int vocab, const int
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = kSampleCluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr; cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, vocab, per, history, history_len,
-                                           history_stride, uniforms, temperature, top_p, min_p, penalty,
-                                           penalty_window, tokens, flags);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, vocab, per, st, temperature, top_p, min_p,
+                                           penalty, penalty_window, tokens, flags);
         if (e == cudaSuccess) return 0;
         if (impl == 2) return fail("sample: the cluster launch failed: %s", cudaGetErrorString(e));
         (void)cudaGetLastError();          // the device cannot place the cluster: one block per row
@@ -899,9 +967,8 @@ extern "C" int mdma_sample(const float* logits, int n_rows, int vocab, const int
         if (e != cudaSuccess) return fail("sample: cannot reserve shared memory: %s", cudaGetErrorString(e));
         configured_one = true;
     }
-    sample_kernel<<<n_rows, kSampleThreads, kWarpHistBytes, stream>>>(logits, vocab, history, history_len, history_stride,
-                                                         uniforms, temperature, top_p, min_p, penalty,
-                                                         penalty_window, probs_scratch, tokens, flags);
+    sample_kernel<<<n_rows, kSampleThreads, kWarpHistBytes, stream>>>(logits, vocab, st, temperature, top_p, min_p, penalty,
+                                                                      penalty_window, probs_scratch, tokens, flags);
     MDMA_LAUNCH_OK("sample");
     return 0;
 }

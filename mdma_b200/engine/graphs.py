@@ -41,6 +41,7 @@ class DecodeSession:
         self.ctx = StepContext(engine.rt, engine.workspace)
         self.steps_done: list[int] = []
         self.launches_per_step = 0          # kernels in one step (counted at the eager first run)
+        self._state_stale, self._use_hist = True, False
         self._bucket = engine.max_context
 
     @property
@@ -55,6 +56,7 @@ class DecodeSession:
         if B == 0 or B > self.engine.max_slots:
             raise StepError(f"a decode session takes 1..{self.engine.max_slots} sequences")
         self.slots = list(slots)
+        self._state_stale = True
         self.requests = list(requests) if requests is not None else list(range(B))
         self.steps_done = list(steps) if steps is not None else [0] * B
         pos = [self.engine.cache.length(s) for s in slots]
@@ -94,11 +96,8 @@ class DecodeSession:
         if p.temperature <= 0.0 and (p.repetition_penalty == 1.0 or p.repetition_window == 0):
             ops.argmax(self.logits[:B], s.tokens, s.flags, B)
         else:
-            hist = s.history if (p.repetition_penalty != 1.0 and p.repetition_window > 0) else None
-            s.ensure_probs()
-            ops.sample(self.logits[:B], s.uniforms, s.tokens, s._probs, p.temperature, p.top_p, p.min_p,
-                       p.repetition_penalty, min(p.repetition_window, s.history_cap), hist,
-                       s.history_len if hist is not None else None, s.flags, B)
+            # uniform numbers, step counts and histories live on the device (see `step_async`)
+            s.sample_resident(self.logits[:B], p, self._use_hist)
         ops.advance_decode(s.tokens, self.ids, self.tok_pos, self.seq_pos0, B)
 
     def step_async(self, histories=None, use_graph: bool = True) -> None:
@@ -110,14 +109,17 @@ class DecodeSession:
         except CacheFull as e:
             raise StepError(str(e)) from None
         p = self.params
-        if p.temperature > 0.0 or (p.repetition_penalty != 1.0 and p.repetition_window > 0):
-            self.sampler.stage_inputs(p, self.requests, self.steps_done, histories)
+        if self._state_stale and (p.temperature > 0.0 or (p.repetition_penalty != 1.0 and p.repetition_window > 0)):
+            # once per batch: requests, step counts and recent tokens go up; from then on the sampling
+            # kernel keeps them (it appends what it selects and counts the steps)
+            self._use_hist = self.sampler.load_state(p, self.requests, self.steps_done, histories)
+        self._state_stale = False
         # kernels choose their grids from an upper bound of the context: the live maximum rounded up
         # to 1024, so a graph stays valid until a sequence grows past its bucket
         longest = max(self.engine.cache.length(s_) for s_ in self.slots) + 1
         self._bucket = min(self.engine.max_context, -(-longest // 1024) * 1024)
         if use_graph and self.graph_safe:
-            g = self.graphs.get((B, self._bucket))
+            g = self.graphs.get((B, self._bucket, self._use_hist))
             if g is None:
                 # The first step at this batch size runs eagerly (it loads kernels and sizes
                 # scratch); the same chain is then captured, without running, for the next ones.
@@ -127,7 +129,7 @@ class DecodeSession:
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     self._body(B)
-                self.graphs[(B, self._bucket)] = g
+                self.graphs[(B, self._bucket, self._use_hist)] = g
             else:
                 g.replay()
         else:

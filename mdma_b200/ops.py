@@ -166,14 +166,22 @@ def sample_scratch_words(n_rows: int, vocab: int) -> int:
     return 3 * n_rows * vocab
 
 
-def sample(logits: torch.Tensor, uniforms: torch.Tensor, tokens: torch.Tensor, probs_scratch: torch.Tensor,
+def sample(logits: torch.Tensor, uniforms: Optional[torch.Tensor], tokens: torch.Tensor, probs_scratch: torch.Tensor,
            temperature: float, top_p: float, min_p: float, penalty: float, penalty_window: int,
            history: Optional[torch.Tensor] = None, history_len: Optional[torch.Tensor] = None,
-           flags: Optional[torch.Tensor] = None, n_rows: Optional[int] = None, impl: int = 0) -> None:
-    """`impl`: 0 picks (a cluster of eight blocks per row when the row fits), 1 one block per row, 2 the cluster."""
-    _need_cuda(logits, uniforms, tokens, probs_scratch, history, history_len, flags)
+           flags: Optional[torch.Tensor] = None, n_rows: Optional[int] = None, impl: int = 0,
+           requests: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None, seed: int = 0,
+           advance: bool = False) -> None:
+    """One token per row of `logits`.  The uniform number of a row is `uniforms[r]`, or, without
+    `uniforms`, made on the device from (seed, requests[r], steps[r]).  `history` [rows, cap] is a ring of
+    recent token ids per row and `history_len` the count of tokens ever added to it.  `advance`: the
+    kernel appends the selected token to the ring and adds one to `steps`.
+    `impl`: 0 picks (a cluster of eight blocks per row when the row fits), 1 one block per row, 2 the cluster."""
+    _need_cuda(logits, uniforms, tokens, probs_scratch, history, history_len, flags, requests, steps)
     assert logits.dtype == torch.float32 and logits.is_contiguous()
-    assert uniforms.dtype == torch.float32 and tokens.dtype == torch.int32
+    assert tokens.dtype == torch.int32 and (uniforms is None or uniforms.dtype == torch.float32)
+    assert uniforms is not None or (requests is not None and steps is not None)
+    assert requests is None or (requests.dtype == torch.int32 and steps.dtype == torch.int32)
     n = logits.shape[0] if n_rows is None else n_rows
     assert probs_scratch.dtype == torch.float32 and probs_scratch.numel() >= sample_scratch_words(n, logits.shape[1])
     hstride = 0
@@ -181,7 +189,8 @@ def sample(logits: torch.Tensor, uniforms: torch.Tensor, tokens: torch.Tensor, p
         assert history.dtype == torch.int32 and history_len.dtype == torch.int32 and history.is_contiguous()
         hstride = history.shape[1]
     _call("core", "mdma_sample", _ptr(logits), _i(n), _i(logits.shape[1]), _ptr(history),
-          _ptr(history_len), _i(hstride), _ptr(uniforms), _f(temperature), _f(top_p), _f(min_p),
+          _ptr(history_len), _i(hstride), _ptr(uniforms), _ptr(requests), _ptr(steps),
+          ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _i(int(advance)), _f(temperature), _f(top_p), _f(min_p),
           _f(penalty), _i(penalty_window), _ptr(probs_scratch), ctypes.c_long(probs_scratch.numel()), _ptr(tokens),
           _ptr(flags), _i(impl), _stream())
 

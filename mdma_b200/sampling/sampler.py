@@ -23,6 +23,10 @@ class DeviceSampler:
         self.history_cap = max(1, history_cap)
         self.history = torch.zeros((max_rows, self.history_cap), dtype=torch.int32, device=device)
         self.history_len = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        # a decode loop that is replayed as a graph keeps what a draw depends on here: the kernel makes
+        # the uniform numbers from (seed, request, step), counts the steps and appends to the histories
+        self.requests = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.steps = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self._probs: Optional[torch.Tensor] = None
         self._out_host = torch.empty(2 * max_rows, dtype=torch.int32).pin_memory()
 
@@ -49,6 +53,23 @@ class DeviceSampler:
             self.history_len[:n].copy_(torch.from_numpy(lens))
             return True
         return False
+
+    def load_state(self, params: SamplingParams, requests, steps, histories=None) -> bool:
+        """Put the rows' requests, step counts and recent tokens on the device, once per batch; after that
+        `sample_resident` needs nothing from the host.  Returns whether histories are in use."""
+        n = len(requests)
+        self.requests[:n].copy_(torch.from_numpy(np.asarray(list(requests), dtype=np.int32)))
+        self.steps[:n].copy_(torch.from_numpy(np.asarray(list(steps), dtype=np.int32)))
+        return self.stage_inputs(params, requests, steps, histories)
+
+    def sample_resident(self, logits: torch.Tensor, params: SamplingParams, use_hist: bool) -> None:
+        """Fill self.tokens/flags for the rows of `logits` from the state that `load_state` left and
+        move it on by one step (graph-safe: no host data)."""
+        self.ensure_probs()
+        ops.sample(logits, None, self.tokens, self._probs, params.temperature, params.top_p, params.min_p,
+                   params.repetition_penalty, min(params.repetition_window, self.history_cap),
+                   self.history if use_hist else None, self.history_len if use_hist else None, self.flags,
+                   logits.shape[0], requests=self.requests, steps=self.steps, seed=params.seed, advance=True)
 
     def sample_device(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
                       steps: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> None:

@@ -57,6 +57,10 @@ def test_sampled_generation_is_seeded_and_independent_of_batch_mates():
     other = mdma_b200.generate(d, prompts, dtype="float32", max_batch=4, **{**kw, "seed": 12})
     f32 = mdma_b200.generate(d, prompts, dtype="float32", max_batch=4, **kw)
     assert [o.tokens for o in other] != [o.tokens for o in f32]
+    # the replayed decode loop keeps step counts, uniform numbers and histories on the device; the
+    # step-by-step loop brings them from the host every step: the same tokens either way
+    eager = mdma_b200.generate(d, prompts, dtype="float32", max_batch=4, use_graphs=False, **kw)
+    assert [o.tokens for o in eager] == [o.tokens for o in f32]
     # request 2 alone, given its place in the list, draws the same tokens as inside the batch
     from mdma_b200.engine import Engine
     from mdma_b200.engine.generate import Generator
@@ -66,7 +70,7 @@ def test_sampled_generation_is_seeded_and_independent_of_batch_mates():
     params = SamplingParams(0.8, 0.95, 0.05, 1.1, 64, 11)
     W = {k: v.float() for k, v in tensors.items()}
     seq = list(prompts[2])
-    for step in range(4):
+    for step in range(8):
         logits = plain_forward(c, W, seq, torch.float32)[-1]
         tok = plain_sample(logits.tolist(), seq, uniform(11, 2, step), 0.8, 0.95, 0.05, 1.1, 64)
         assert tok == f32[2].tokens[step], step
