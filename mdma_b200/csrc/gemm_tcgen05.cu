@@ -754,9 +754,12 @@ int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_coun
         *bn_out = bn; *splits_out = -2; return 0;
     }
     if (mode != kTcSwiGLU && tiles < sm_count) {
-        // As many blocks as can be resident at once (two per SM), not more: measured at the 8B decode
-        // shapes, 288 blocks beat 192 and 160, and anything beyond 296 is slower again.
-        splits = (int)((2 * sm_count) / tiles);
+        // As many blocks as can be resident at once, not more: two per SM for token tiles up to 64
+        // (measured at the 8B decode shapes, 288 blocks beat 192 and 160, and anything beyond 296 is
+        // slower again), one per SM for larger tiles, which take the whole shared memory (128 tokens:
+        // QKV 14.5 us with 3 splits against 21.8 us with 6, O 12.3 against 19.5, down 26.9 against 34.8).
+        splits = (int)(((bn <= 64 ? 2 : 1) * sm_count) / tiles);
+        if (splits < 1) splits = 1;
         if (splits > 16) splits = 16;
         if (splits > k_blocks / 4) splits = k_blocks / 4 > 0 ? k_blocks / 4 : 1;
     }
