@@ -653,13 +653,10 @@ __device__ ClusterCrossing find_crossing_cluster(const float* slice, int n, int 
     __syncthreads();
     if (threadIdx.x == 0) xch->ties = misc[1];
     ptx::cluster_sync();
-    int before = 0, all_ties = 0, owner = -1;
+    int all_ties = 0, owner = -1;
     long long before_owner = 0;
-    for (int k = 0; k < kSampleCluster; ++k) {
-        const int t = (int)ptx::cluster_load_u32(ptx::cluster_map(xch_addr + (uint32_t)offsetof(SampleExchange, ties), k));
-        if (k < rank) before += t;
-        all_ties += t;
-    }
+    for (int k = 0; k < kSampleCluster; ++k)
+        all_ties += (int)ptx::cluster_load_u32(ptx::cluster_map(xch_addr + (uint32_t)offsetof(SampleExchange, ties), k));
     if (all_ties > 0 && kth > all_ties) kth = all_ties;          // fewer ties than asked for (rounding): the last one
     {
         int run = 0;
@@ -695,7 +692,6 @@ __device__ ClusterCrossing find_crossing_cluster(const float* slice, int n, int 
             __syncthreads();
         }
     }
-    (void)before;
     ptx::cluster_sync();
     ClusterCrossing c;
     c.index = owner >= 0 ? (int)ptx::cluster_load_u32(ptx::cluster_map(xch_addr + (uint32_t)offsetof(SampleExchange, answer), owner))
@@ -935,11 +931,9 @@ extern "C" int mdma_sample(const float* logits, int n_rows, int vocab, int* hist
     MDMA_REQUIRE(penalty > 0.f, "sample: repetition penalty must be positive");
     if (n_rows == 0) return 0;
     // A cluster of eight blocks per row when an eighth of the row fits a block's shared memory
-    // (vocabularies up to about 400k); else, or if `impl` asks for it, one block per row.
+    // (vocabularies up to about 250k); else, or if `impl` asks for it, one block per row.
     const int per = ((vocab + kSampleCluster - 1) / kSampleCluster + 3) / 4 * 4;
     const size_t slice_bytes = (size_t)per * sizeof(float) + kWarpHistBytes;
-    const bool aligned = vocab % 4 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
-    (void)aligned;
     if (impl != 1 && slice_bytes <= 220 * 1024 && n_rows <= 65535) {
         static bool configured = false;
         if (!configured) {
