@@ -138,3 +138,34 @@ def test_truncate_gives_pages_back_and_refuses_what_cannot_be_rewound():
     t = stateful.acquire()
     with pytest.raises(ValueError, match="state"):
         stateful.truncate(t, 0)
+
+
+def test_token_by_token_growth_holds_exactly_the_pages_it_needs():
+    """A sequence that grows one token a step (decoding) looks only at its newest page each step; the pages it
+    ends up with are the ones a single extension to the same length would take, also with a window and
+    after a rewind."""
+    for window in (0, 100):
+        c = make_cache(window=window, max_tokens=64 * 24, slots=2, ctx=700)
+        a, b = c.acquire(), c.acquire()
+        c.extend({a: 130}); c.commit({a: 130})
+        for _ in range(300):
+            c.extend({a: 1}); c.commit({a: 1})
+        c.extend({b: 430}); c.commit({b: 430})
+        c.check()
+        for g in c.groups:
+            pages_a, pages_b = set(g.seq_pages[a]), set(g.seq_pages[b])
+            if g.need.window:
+                # what has left the window is given back; what is kept covers the window and the newest page
+                first_live = max(0, 430 + 1 - g.need.window) // 64
+                assert pages_a == set(range(first_live, (430 - 1) // 64 + 1))
+                assert pages_b >= pages_a
+            else:
+                assert pages_a == pages_b == set(range((430 - 1) // 64 + 1))
+    c = SequenceCache([KVNeed(2, 16, 0)], [None], 64 * 24, 1, 700, torch.float32, "cpu", page_size=64)    # no state: may rewind
+    a = c.acquire()
+    c.extend({a: 200}); c.commit({a: 200})
+    c.truncate(a, 70)
+    for _ in range(100):
+        c.extend({a: 1}); c.commit({a: 1})
+    c.check()
+    assert all(set(g.seq_pages[a]) == {0, 1, 2} for g in c.groups)
