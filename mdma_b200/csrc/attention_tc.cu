@@ -76,7 +76,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     chain_release();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int seq = blockIdx.y, kvh = blockIdx.z;
+    const int seq = blockIdx.y, kvh = blockIdx.x;
     if (threadIdx.x == 0) {
         if (base & 1023u) *abort_flag = 1;          // the tiles need 1024-byte alignment (checked again below)
         ptx::mbar_init(q_full, 1);
@@ -102,8 +102,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     chain_wait();
     const int row0_seq = p.seq_start[seq];
     const int n_new = p.seq_start[seq + 1] - row0_seq;
-    // late tiles see the most keys: they are handed out first so that the short ones fill the tail
-    const int tok0 = (int)(gridDim.x - 1 - blockIdx.x) * p.tile_tokens;
+    // late tiles see the most keys: they are handed out first so that the short ones fill the tail.  The
+    // kv heads (and sequences) run fastest in the grid: blocks that run side by side then read different
+    // keys and values (with the tiles of ONE head side by side, all on the same lines of L2, the kernel
+    // took 72 us instead of 54 us for 2,048 tokens)
+    const int tok0 = (int)(gridDim.z - 1 - blockIdx.z) * p.tile_tokens;
     const bool active = tok0 < n_new && !(base & 1023u);      // uniform over the block
     const int n_tok = active ? min(p.tile_tokens, n_new - tok0) : 0;
     const int pos0 = p.seq_pos0[seq] + tok0;
@@ -427,7 +430,7 @@ int mdma_attention_tc(const void* q, int q_stride, int q_rows_cap, const void* k
         if (e != cudaSuccess) return fail("attention_tc: cannot reserve %d bytes of shared memory: %s", kAttnTcSmem, cudaGetErrorString(e));
         once = true;
     }
-    dim3 grid((max_new + p.tile_tokens - 1) / p.tile_tokens, n_seqs, n_kv_heads);
+    dim3 grid(n_kv_heads, n_seqs, (max_new + p.tile_tokens - 1) / p.tile_tokens);
     cudaError_t e = launch_chained(attention_tc_kernel, grid, dim3(kTcThreadsA), kAttnTcSmem, stream, mq, mk, mv, p);
     if (e != cudaSuccess) return fail("attention_tc: launch failed: %s", cudaGetErrorString(e));
     return 0;
