@@ -1,0 +1,37 @@
+"""What bench.py answers without a GPU: more than one GPU, and the reference arm."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run(*args):
+    return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True,
+                          cwd=ROOT, timeout=120)
+
+
+def test_more_than_one_gpu_is_refused_in_one_line():
+    r = run("--gpus", "2", "--steps", "4", "--warmup", "3")
+    assert r.returncode == 2
+    lines = [l for l in r.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1 and "one GPU" in lines[0]
+
+
+def test_reference_arm_says_why_it_is_unavailable():
+    r = run("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3")
+    assert r.returncode == 0
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    assert d["impl"] == "reference" and isinstance(d["unavailable"], str) and "\n" not in d["unavailable"]
+
+
+def test_shapes_are_those_of_one_architecture():
+    sys.path.insert(0, ROOT)
+    import bench
+    from mdma_b200.config import LlamaConfig
+    assert set(bench.SHAPES) == {"llama-3.1-8b", "llama-2-7b", "llama-3.2-1b"}
+    for name, (label, cfg) in bench.SHAPES.items():
+        c = LlamaConfig.from_dict(cfg)            # every shape is a valid configuration of the architecture
+        assert c.num_attention_heads % c.num_key_value_heads == 0 and label
+    assert bench.SHAPES["llama-3.1-8b"][1]["num_hidden_layers"] == 32
