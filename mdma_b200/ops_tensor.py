@@ -35,6 +35,7 @@ def check_status(device: torch.device) -> None:
     st = _state.get(device.index)
     if st is not None and int(st["status"][0].item()) != 0:
         st["status"].zero_()
+        st["sk_flags"].zero_()          # a block pair that gave up may have left its flag standing
         raise KernelError("a tensor-core kernel ran into its wait limit; its output is not valid")
 
 
