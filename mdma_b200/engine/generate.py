@@ -97,6 +97,9 @@ class Generator:
         params = params or SamplingParams.greedy()
         params.validate()
         stop = frozenset(int(s) for s in stop_ids)
+        if params.repetition_penalty != 1.0 and hasattr(self.sampler, "ensure_history"):
+            if self.sampler.ensure_history(params.repetition_window):
+                self._sessions.clear()          # their graphs hold the old history buffers
         budgets = [token_budget(len(p), max_tokens, self.engine.max_context) for p in prompts]
         outputs = [Output(list(p)) for p in prompts]
         sizes = [(len(p), b) for p, (b, _) in zip(prompts, budgets)]

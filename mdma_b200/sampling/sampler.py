@@ -30,6 +30,16 @@ class DeviceSampler:
         self._probs: Optional[torch.Tensor] = None
         self._out_host = torch.empty(2 * max_rows, dtype=torch.int32).pin_memory()
 
+    def ensure_history(self, window: int) -> bool:
+        """Room for the last `window` tokens of every row.  Returns True if the buffers were replaced
+        (graphs that captured the old ones must not be replayed)."""
+        if window <= self.history_cap:
+            return False
+        self.history_cap = window
+        self.history = torch.zeros((self.max_rows, window), dtype=torch.int32, device=self.device)
+        self.history_len.zero_()
+        return True
+
     def ensure_probs(self) -> None:
         if self._probs is None:
             self._probs = torch.empty(ops.sample_scratch_words(self.max_rows, self.vocab), dtype=torch.float32,

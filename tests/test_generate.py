@@ -77,6 +77,27 @@ def test_sampled_generation_is_seeded_and_independent_of_batch_mates():
         seq.append(tok)
 
 
+def test_repetition_window_longer_than_the_default_history():
+    """A window of 100 tokens: the sampler's per-row history grows to hold it, in the replayed loop and in
+    the step-by-step loop, and the tokens follow the plain sampler with that window."""
+    import mdma_b200
+    from mdma_b200.sampling import uniform
+    d, c, tensors = make_model(TINY_B, 1, torch.bfloat16)
+    prompts = prompts_for(TINY_B, (120, 90), 3)
+    kw = dict(max_tokens=12, temperature=0.9, top_p=0.9, min_p=0.02, repetition_penalty=1.4, repetition_window=100, seed=5,
+              dtype="float32", max_batch=2)
+    got = mdma_b200.generate(d, prompts, **kw)
+    eager = mdma_b200.generate(d, prompts, use_graphs=False, **kw)
+    assert [o.tokens for o in got] == [o.tokens for o in eager]
+    W = {k: v.float() for k, v in tensors.items()}
+    seq = list(prompts[0])
+    for step in range(6):
+        logits = plain_forward(c, W, seq, torch.float32)[-1]
+        tok = plain_sample(logits.tolist(), seq, uniform(5, 0, step), 0.9, 0.9, 0.02, 1.4, 100)
+        assert tok == got[0].tokens[step], step
+        seq.append(tok)
+
+
 def test_command_line(tmp_path):
     d, c, tensors = make_model(TINY_A, 0, torch.float32)
     p = prompts_for(TINY_A, (6,), 3)[0]
