@@ -155,7 +155,6 @@ def main() -> int:
     from mdma_b200.engine import Engine, StepEntry
     from mdma_b200.engine.generate import Generator
     from mdma_b200.sampling import SamplingParams
-    from mdma_b200.sampling.sampler import DeviceSampler
 
     shape_name, shape_cfg = SHAPES[args.shape]
     FULL_LAYERS = shape_cfg["num_hidden_layers"]
@@ -167,7 +166,7 @@ def main() -> int:
     max_batch = max(args.batch, 1 if args.no_points else 64)
     eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_batch=max_batch,
                  max_context=max(args.context, args.prefill_tokens))
-    sampler = DeviceSampler(eng.vocab_size, eng.max_slots, eng.device)
+    sampler = eng.sampler
     gen = torch.Generator().manual_seed(0)
 
     def prompts(n, length):
@@ -179,16 +178,16 @@ def main() -> int:
         ps = prompts(batch, args.prompt_len)
         logits = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, ps)])
         toks, _ = sampler.sample(logits, SamplingParams.greedy(), list(range(batch)), [0] * batch)
-        sess = eng.decode_session(sampler, SamplingParams.greedy())
+        sess = eng.decode_session()
         sess.start(slots, toks)
         for _ in range(warmup):
-            sess.step_async()
+            sess.run(1)
         torch.cuda.synchronize()
-        launches0 = ops.LAUNCHES
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
-            sess.step_async()
+        done = 0
+        while done < steps:             # exactly `steps` steps, replayed in runs as generation does
+            done += sess.run(min(sess.max_run, steps - done))
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
@@ -233,15 +232,25 @@ def main() -> int:
     e2e = None
     if not args.no_e2e:
         stamps = []
-        g = Generator(eng, sampler)
+        g = Generator(eng)
         n_e2e = args.steps + warmup + 1
-        g.generate(prompts(args.batch, args.prompt_len), max_tokens=warmup + 2)        # warm the path
+        g.generate(prompts(args.batch, args.prompt_len), max_tokens=2 * g.run_ahead + 2)        # warm the path
+        up0, down0 = eng.h2d_bytes, eng.d2h_bytes + sampler.d2h_bytes
+        t_start = time.perf_counter()
         g.generate(prompts(args.batch, args.prompt_len), max_tokens=n_e2e,
                    on_token=lambda r, t: stamps.append(time.perf_counter()) if r == args.batch - 1 else None)
-        # stamps[i] is taken after every sequence's i-th token reached the host
-        e2e_value = args.batch * args.steps / (stamps[-1] - stamps[-1 - args.steps])
-        e2e = {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
-               "d2h_bytes_per_step": 8 * sampler.max_rows}      # tokens and flags of every sampler row, one copy
+        # Host token lists go in, host token lists come out.  The tokens of `run_ahead` replayed steps reach
+        # the host in one copy, so the rate is taken over the whole call but for the prompt step: from the
+        # moment the first tokens are on the host to the moment the last ones are.
+        e2e_value = args.batch * (len(stamps) - 1) / (stamps[-1] - stamps[0])
+        n_steps = len(stamps) - 1
+        e2e = {"value": round(e2e_value, 2), "unit": "tokens/s",
+               # counted from the tensors copied during the call (prompt ids and step metadata up from pinned
+               # memory; tokens, flags and the kernels' status word down), divided by its decode steps
+               "h2d_bytes_per_step": round((eng.h2d_bytes - up0) / n_steps, 1),
+               "d2h_bytes_per_step": round((eng.d2h_bytes + sampler.d2h_bytes - down0) / n_steps, 1),
+               "steps": n_steps, "run_ahead": g.run_ahead,
+               "with_prompt_step": round(args.batch * len(stamps) / (stamps[-1] - t_start), 2)}
 
     out = {
         "metric": f"decode tokens/s ({shape_name}, batch {args.batch}, after {args.prompt_len}-token prompts)",
@@ -271,8 +280,7 @@ def main() -> int:
         out["points"] = points
         out["prefill"] = time_prefill()
     out["clocks"] = clock.stop()
-    from mdma_b200 import ops_tensor
-    ops_tensor.check_status(eng.device)
+    eng.check_status()
     print(json.dumps(out))
     return 0
 

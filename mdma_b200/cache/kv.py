@@ -55,7 +55,7 @@ class KVView:
 
 class CacheGroup:
     def __init__(self, need: KVNeed, sites: list[int], n_pages: int, n_slots: int, max_pages: int,
-                 page_size: int, dtype: torch.dtype, device, allocate: bool = True):
+                 page_size: int, dtype: torch.dtype, alloc):
         self.need, self.sites = need, sites
         self.n_pages, self.page_size, self.max_pages = n_pages, page_size, max_pages
         self.pages = FreeList(n_pages, "cache page")
@@ -64,11 +64,10 @@ class CacheGroup:
         self.dirty: set[int] = set()
         shape = (len(sites), n_pages, page_size, need.n_kv_heads, need.head_dim)
         self.bytes = 2 * int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
-        self.k = self.v = self.table_dev = None
-        if allocate:
-            self.k = torch.zeros(shape, dtype=dtype, device=device)
-            self.v = torch.zeros(shape, dtype=dtype, device=device)
-            self.table_dev = torch.zeros((n_slots, max_pages), dtype=torch.int32, device=device)
+        # `alloc(shape, dtype)` hands out zeroed device memory, or None when only sizes are wanted
+        self.k = alloc(shape, dtype)
+        self.v = alloc(shape, dtype)
+        self.table_dev = alloc((n_slots, max_pages), torch.int32)
 
     def grow(self, slot: int, old_len: int, new_len: int) -> None:
         """Make sure pages cover positions [.., new_len) of `slot` for this step."""
@@ -110,10 +109,8 @@ class CacheGroup:
         """Copy the page-table rows that changed to the device."""
         if self.table_dev is None or not self.dirty:
             return
-        rows = sorted(self.dirty)
-        idx = torch.as_tensor(rows, dtype=torch.long)
-        src = torch.from_numpy(self.table_host[rows]).to(self.table_dev.device, non_blocking=False)
-        self.table_dev.index_copy_(0, idx.to(self.table_dev.device), src)
+        for row in sorted(self.dirty):      # straight into the table: no device memory is taken for the copy
+            self.table_dev[row].copy_(torch.from_numpy(self.table_host[row]))
         self.dirty.clear()
 
 
@@ -122,8 +119,14 @@ class SequenceCache:
 
     def __init__(self, kv_needs: list[Optional[KVNeed]], state_needs: list[Optional[StateNeed]],
                  max_tokens: int, max_slots: int, max_context: int, dtype: torch.dtype, device,
-                 page_size: int = 64, allocate: bool = True):
+                 page_size: int = 64, allocate: bool = True, alloc=None):
+        """`alloc(shape, dtype)`: where pools, tables and state come from (an engine passes its arena;
+        it may return None to add up sizes only).  Without it they are allocated here, or, with
+        `allocate=False`, not at all."""
         assert len(kv_needs) == len(state_needs)
+        if alloc is None:
+            alloc = ((lambda shape, dt: torch.zeros(shape, dtype=dt, device=device)) if allocate
+                     else (lambda shape, dt: None))
         if page_size <= 0 or max_tokens <= 0 or max_slots <= 0 or max_context <= 0:
             raise ValueError("cache sizes must be positive")
         self.page_size, self.max_context, self.max_slots = page_size, max_context, max_slots
@@ -139,8 +142,7 @@ class SequenceCache:
             if need is not None:
                 by_need.setdefault(need, []).append(site)
         for need, sites in by_need.items():
-            g = CacheGroup(need, sites, self.n_pages, max_slots, self.max_pages, page_size, dtype,
-                           device, allocate)
+            g = CacheGroup(need, sites, self.n_pages, max_slots, self.max_pages, page_size, dtype, alloc)
             for j, site in enumerate(sites):
                 self.site_group[site] = (len(self.groups), j)
             self.groups.append(g)
@@ -151,8 +153,9 @@ class SequenceCache:
                 continue
             n = int(np.prod(need.shape)) * max_slots * torch.empty((), dtype=need.dtype).element_size()
             self.state_bytes += n
-            if allocate:
-                self.states[site] = torch.zeros((max_slots, *need.shape), dtype=need.dtype, device=device)
+            state = alloc((max_slots, *need.shape), need.dtype)
+            if state is not None:
+                self.states[site] = state
 
     # ---- sizes ---------------------------------------------------------
     @property
@@ -247,6 +250,28 @@ class SequenceCache:
         g = self.groups[gi]
         return KVView(g.k[j] if g.k is not None else None, g.v[j] if g.v is not None else None,
                       g.table_dev, self.page_size, self.max_pages, g.need.window, state)
+
+    def poison_unused(self, value: float = float("nan")) -> None:
+        """Testing aid: overwrite every cache row that no live sequence owns (all rows of free
+        pages, and the rows at and beyond each sequence's length in the pages it holds) with
+        `value`.  Results must not change: a kernel may fetch such rows with a tile but must not
+        let them reach its output (the reference's rule is `written` against `len`,
+        src/kv_cache.rs:246-268)."""
+        for g in self.groups:
+            if g.k is None:
+                continue
+            free = sorted(set(range(g.n_pages)) - set(g.pages.held))
+            if free:
+                idx = torch.as_tensor(free, dtype=torch.long, device=g.k.device)
+                g.k.index_fill_(1, idx, value)
+                g.v.index_fill_(1, idx, value)
+            for slot, have in g.seq_pages.items():
+                length = self.lengths.get(slot, 0)
+                for p, page in have.items():
+                    first = max(0, length - p * self.page_size)
+                    if first < self.page_size:
+                        g.k[:, page, first:] = value
+                        g.v[:, page, first:] = value
 
     def check(self) -> None:
         """Invariants: no slot or page lost, held twice, or owned by two sequences."""

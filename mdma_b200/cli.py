@@ -36,7 +36,6 @@ def cmd_run(args) -> int:
     from .engine.generate import Generator
     from .engine.step import Engine, MemoryBudgetError
     from .sampling import SamplingParams
-    from .sampling.sampler import DeviceSampler
     prompts = [args.prompt] + list(args.more_prompts or [])
     if args.max_tokens <= 0:
         print("--max-tokens must be positive", file=sys.stderr)
@@ -45,7 +44,8 @@ def cmd_run(args) -> int:
     try:
         engine = Engine(args.model, dtype=args.dtype, max_batch=min(args.max_batch, len(prompts)),
                         max_context=args.max_context or None, reserve_mib=args.reserve_mib,
-                        vram_bytes=args.vram_bytes, context_hint=need_ctx)
+                        vram_bytes=args.vram_bytes, context_hint=need_ctx,
+                        history_cap=max(64, args.repetition_window))
     except MemoryBudgetError as e:
         print(f"model/request does not fit the device budget: {e}", file=sys.stderr)
         return 1
@@ -55,8 +55,7 @@ def cmd_run(args) -> int:
         params = SamplingParams(args.temperature, args.top_p, args.min_p, args.repetition_penalty,
                                 args.repetition_window, args.seed)
     stop = parse_ids(args.stop_ids) if args.stop_ids else list(engine.spec.stop_token_ids)
-    sampler = DeviceSampler(engine.vocab_size, engine.max_slots, engine.device)
-    outs = Generator(engine, sampler).generate(prompts, args.max_tokens, params, stop)
+    outs = Generator(engine).generate(prompts, args.max_tokens, params, stop)
     for o in outs:
         if args.json or os.environ.get("MDMA_JSON") is not None:
             print(json.dumps({"prompt_tokens": o.prompt_tokens, "tokens": o.tokens,

@@ -114,7 +114,9 @@ attention_mma_kernel(const AttnParams p) {
         for (int i = threadIdx.x; i < kKeys * kChunks; i += kAttnThreads) {
             const int r = i / kChunks, c = i % kChunks;
             const int key = blk * kKeys + r;
-            const bool valid = key <= last_pos && c < d_chunks;
+            // keys outside [first_key, last_pos] are zero-filled, never read: their cache rows may be stale
+            // (another sequence's, or not finite) and 0 * NaN would reach the output through P V
+            const bool valid = key <= last_pos && key >= first_key && c < d_chunks;
             size_t off = 0;
             if (valid) {
                 const int page = pages[key / p.page_size];
@@ -308,7 +310,7 @@ attention_decode_kernel(const AttnParams p) {
         for (int i = lane; i < KB * kChunks; i += 32) {
             const int r = i / kChunks, c = i % kChunks;
             const int key = blk * KB + r;
-            const bool valid = key <= pos && c < d_chunks;
+            const bool valid = key <= pos && key >= first_key && c < d_chunks;      // rows outside are zero-filled
             size_t off = 0;
             if (valid) {
                 if (page_aligned) off = ((base + (size_t)r * p.n_kv_heads) + kvh) * D + c * 8;
@@ -606,6 +608,20 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             o[n][0] *= corr_lo; o[n][1] *= corr_lo; o[n][2] *= corr_hi; o[n][3] *= corr_hi;
         }
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(vbar, phase, abort_flag))) break;     // this tile's V has landed
+        {
+            // A tile is fetched whole.  Rows of keys outside [first_key, pos] belong to nobody (stale rows of
+            // an earlier sequence, possibly not finite): their probabilities are zero, but 0 * NaN is NaN, so
+            // their value rows are cleared before the product.  Only the first and the last tile have any.
+            const int r_lo = first_key - blk * KB, r_hi = pos - blk * KB;      // rows [r_lo, r_hi] are real
+            if (r_lo > 0 || r_hi < KB - 1) {
+                for (int i = lane; i < halves * KB * 8; i += 32) {
+                    const int h = i / (KB * 8), r = (i >> 3) % KB, c = i & 7;
+                    if (r < r_lo || r > r_hi)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sV + h * kHalf + r * 128 + c * 16), "r"(0u) : "memory");
+                }
+                __syncwarp();
+            }
+        }
 #pragma unroll
         for (int kk = 0; kk < KB / 16; ++kk) {
 #pragma unroll
@@ -784,8 +800,9 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
         };
         int rc;
         // few blocks: eight warps each (one block per SM); many: four warps and three blocks per SM
-        static int sm_count = 0;
-        if (sm_count == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
+        int sm_count = 0, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         const bool wide = splits == 1 && (long)n_seqs * n_kv_heads < 2l * sm_count;
         if (wide && head_dim <= 64) rc = launch(attention_decode_tma_kernel<64, kDecodeKeys, 8>, 8, 64);
         else if (wide) rc = launch(attention_decode_tma_kernel<128, kDecodeKeys, 8>, 8, 128);
@@ -796,24 +813,20 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
         // one token per sequence: the decode kernel (no padding rows beyond one 16-row tile)
         if (head_dim <= 64) {
             constexpr int bytes = 16 * 64 * 2 + 4 * 2 * kDecodeKeys * 64 * 2;
-            static bool once = false;
-            if (!once) { cudaFuncSetAttribute(attention_decode_kernel<64, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
+            cudaFuncSetAttribute(attention_decode_kernel<64, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);      // per launch: the attribute belongs to the current device
             launch_chained(attention_decode_kernel<64, kDecodeKeys>, grid, dim3(kAttnThreads), bytes, stream, p);
         } else {
             constexpr int bytes = 16 * 128 * 2 + 4 * 2 * kDecodeKeys * 128 * 2;
-            static bool once = false;
-            if (!once) { cudaFuncSetAttribute(attention_decode_kernel<128, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
+            cudaFuncSetAttribute(attention_decode_kernel<128, kDecodeKeys>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);      // per launch: the attribute belongs to the current device
             launch_chained(attention_decode_kernel<128, kDecodeKeys>, grid, dim3(kAttnThreads), bytes, stream, p);
         }
     } else if (head_dim <= 64) {
         constexpr int bytes = 5 * kRows * 64 * 2;
-        static bool once = false;
-        if (!once) { cudaFuncSetAttribute(attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
+        cudaFuncSetAttribute(attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);      // per launch: the attribute belongs to the current device
         launch_chained(attention_mma_kernel<64>, grid, dim3(kAttnThreads), bytes, stream, p);
     } else {
         constexpr int bytes = 5 * kRows * 128 * 2;
-        static bool once = false;
-        if (!once) { cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); once = true; }
+        cudaFuncSetAttribute(attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);      // per launch: the attribute belongs to the current device
         launch_chained(attention_mma_kernel<128>, grid, dim3(kAttnThreads), bytes, stream, p);
     }
     MDMA_LAUNCH_OK("attention_mma");

@@ -289,6 +289,24 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     ptx::tmem_store_wait();
                 }
             }
+            {
+                // Value rows of keys that no row of this tile may see (beyond its last position, before its
+                // window) belong to nobody: stale rows of an earlier sequence, possibly not finite.  Their
+                // probabilities are zero, but 0 * NaN is NaN, so the rows are cleared in shared memory before
+                // the product reads them.  Only the first and the last key block of a tile have any.
+                const int kb0 = (b0 + i) * kTcKeys;
+                if (kb0 + kTcKeys - 1 > last_pos || kb0 < first_key) {
+                    const int vs = i % kKvStages;
+                    ok = __all_sync(0xffffffffu, ptx::mbar_wait(v_full(vs), (i / kKvStages) & 1, abort_flag));
+                    if (!ok) break;
+                    const int tid = (warp - 2) * 32 + lane;
+                    for (int e = tid; e < halves * kTcKeys * 8; e += 256) {
+                        const int h = e / (kTcKeys * 8), kr = (e >> 3) % kTcKeys, c = e & 7;
+                        if (kb0 + kr > last_pos || kb0 + kr < first_key)
+                            *reinterpret_cast<uint4*>(base_ptr + kSmemV + (vs * 2 + h) * kKvHalf + kr * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
 #pragma unroll
             for (int c = 0; c < 4; ++c) {    // this half's 32 bf16 = 4 chunks of 16 bytes; chunk c of the row sits at c ^ (row & 7)
                 const int cc = half * 4 + c;

@@ -28,7 +28,7 @@ LIBRARIES = {
     # name: (sources, headers, link flags)
     "core": (["elementwise.cu", "gemm_simt.cu", "attention_simple.cu", "sampling.cu"], ["common.cuh"], []),
     "tensor": (["gemm_tcgen05.cu", "attention_mma.cu", "attention_tc.cu"], ["common.cuh", "ptx.cuh", "attention_mma.cuh"], []),
-    "noalloc": (["attention_noalloc.cu"], ["common.cuh", "attention_mma.cuh", "attention_noalloc.h"], []),
+    "noalloc": (["attention_noalloc.cu"], ["common.cuh", "ptx.cuh", "attention_mma.cuh", "attention_noalloc.h"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

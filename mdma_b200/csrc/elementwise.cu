@@ -302,16 +302,26 @@ __global__ void rope_cache_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, int
 }
 
 // After a decode step: the sampled tokens become the next inputs and every
-// position moves on by one.
+// position moves on by one.  With a ring, the step's result words (tokens, flags and
+// what lies behind them: `out_words` integers) are also kept in row `*counter % ring_rows`
+// of the ring and the counter moves on, so that several steps can run before the host
+// reads their tokens in one copy.  One block.
 __global__ void advance_decode_kernel(const int* __restrict__ tokens, int* __restrict__ ids,
-                                      int* __restrict__ tok_pos, int* __restrict__ seq_pos0, int n) {
+                                      int* __restrict__ tok_pos, int* __restrict__ seq_pos0, int n,
+                                      int out_words, int* __restrict__ ring, int ring_rows, int* __restrict__ counter) {
     chain_release();
     chain_wait();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    ids[i] = tokens[i];
-    tok_pos[i] += 1;
-    seq_pos0[i] += 1;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        ids[i] = tokens[i];
+        tok_pos[i] += 1;
+        seq_pos0[i] += 1;
+    }
+    if (ring != nullptr) {
+        const int row = *counter % ring_rows;
+        for (int i = threadIdx.x; i < out_words; i += blockDim.x) ring[(size_t)row * out_words + i] = tokens[i];
+        __syncthreads();                 // every thread has read the counter
+        if (threadIdx.x == 0) *counter += 1;
+    }
 }
 
 template <typename TO, typename TW>
@@ -343,15 +353,54 @@ static void launch_rmsnorm(float* x, const float* partial, int splits, size_t sp
         launch_chained(rmsnorm_kernel<TO, TW, 0>, dim3(n_rows), dim3(1024), 0, stream, x, partial, splits, split_stride, w, rows, y, width, eps);
 }
 
+// Seeded normal numbers that the host can reproduce bit for bit: element i of a tensor takes 24 bits of
+// a counter-based hash of (key, i) (two rounds of splitmix64); 16 of them pick an interval of a table
+// of 65,537 normal quantiles that the host computed, 8 the place inside it.  Every floating-point step
+// is a single correctly rounded operation (no fused multiply-add), as on the host.
+__device__ __forceinline__ unsigned long long fill_mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+template <typename T>
+__global__ void fill_normal_kernel(T* __restrict__ out, long n, unsigned long long key,
+                                   const float* __restrict__ table, float std) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const unsigned long long z = fill_mix64(fill_mix64(key ^ (unsigned long long)i));
+        const int j = (int)(z >> 48);
+        const float f = (float)((z >> 40) & 0xFFull) * (1.0f / 256.0f);
+        const float lo = table[j];
+        const float v = __fadd_rn(lo, __fmul_rn(__fsub_rn(table[j + 1], lo), f));
+        out[i] = from_float<T>(__fmul_rn(v, std));
+    }
+}
+
 }  // namespace mdma
 
 using namespace mdma;
 
 extern "C" {
 
-int mdma_advance_decode(const int* tokens, int* ids, int* tok_pos, int* seq_pos0, int n, cudaStream_t stream) {
+// out[i] = std * quantile(hash(key, i)) for i < n; `table` holds 65,537 floats on the device.
+int mdma_fill_normal(void* out, int dtype, long n, unsigned long long key, const float* table, float std,
+                     cudaStream_t stream) {
+    MDMA_REQUIRE(out && table && n >= 0, "fill_normal: bad arguments");
+    if (n == 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    MDMA_DISPATCH_DTYPE(dtype, T, (fill_normal_kernel<T><<<blocks, 256, 0, stream>>>((T*)out, n, key, table, std)));
+    MDMA_LAUNCH_OK("fill_normal");
+    return 0;
+}
+
+// `tokens` is the start of the sampler's result words (tokens first); `ring` (optional) has
+// `ring_rows` rows of `out_words` integers, `counter` counts the steps kept so far.
+int mdma_advance_decode(const int* tokens, int* ids, int* tok_pos, int* seq_pos0, int n, int out_words,
+                        int* ring, int ring_rows, int* counter, cudaStream_t stream) {
     if (n <= 0) return 0;
-    launch_chained(advance_decode_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, ids, tok_pos, seq_pos0, n);
+    MDMA_REQUIRE(ring == nullptr || (ring_rows > 0 && counter != nullptr && out_words >= n), "advance_decode: bad ring");
+    launch_chained(advance_decode_kernel, dim3(1), dim3(256), 0, stream, tokens, ids, tok_pos, seq_pos0, n,
+                   out_words, ring, ring_rows, counter);
     MDMA_LAUNCH_OK("advance_decode");
     return 0;
 }

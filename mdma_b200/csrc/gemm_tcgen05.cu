@@ -827,8 +827,12 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     splits = (k_blocks + p.kb_per_split - 1) / p.kb_per_split;     // no empty split
     p.partial = nullptr; p.status = status; p.cluster = 1; p.sk_partial = nullptr; p.sk_flags = nullptr;
     if (bn == 512) {           // the two-block kernel (a pair covers 256 features x 256 tokens)
-        // scratch: partial tiles (148 x accumulators x 256 x 128 floats), then 148 integer flags that are zero between launches
-        const long part_floats = 148l * (mode == kTcSwiGLU ? 2 : 1) * 256 * 128;
+        // scratch: one partial tile per block of every pair (accumulators x 256 x 128 floats each); the flags,
+        // one per block, are zero between launches
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long part_floats = (long)sms * (mode == kTcSwiGLU ? 2 : 1) * 256 * 128;
         p.sk_partial = nullptr; p.sk_flags = nullptr;
         if (sk_flags != nullptr && scratch != nullptr && scratch_floats >= part_floats) { p.sk_partial = scratch; p.sk_flags = sk_flags; }
         if (mode == kTcStore) return run_tc2<kTcStore>(x, ldx, w, w2, K, p, stream);

@@ -242,12 +242,26 @@ __device__ __forceinline__ void pick_digit(const unsigned long long* bins, unsig
 // not matter: a token is divided or multiplied once per occurrence).  With `advance` the kernel
 // appends the token it selected to the ring and moves the row's step counter on, so that a decode loop
 // replayed as a graph needs nothing from the host between steps.
+// `dev_params`, when given, overrides the options passed by value with eight words read from device
+// memory: temperature, top_p, min_p, penalty (floats), penalty window (int), one unused word, the seed's
+// low and high halves.  A decode loop captured in a graph then serves every request's options and seed:
+// the host rewrites the words between batches and replays the same graph.
 struct SampleState {
     int* history; int* history_len; int history_stride;
     const float* uniforms;
     const int* requests; int* steps; unsigned long long seed;
     int advance;
+    const unsigned* dev_params;
 };
+__device__ __forceinline__ void load_device_params(const SampleState& st, float& temperature, float& top_p,
+                                                   float& min_p, float& penalty, int& penalty_window) {
+    if (st.dev_params == nullptr) return;
+    temperature = __uint_as_float(st.dev_params[0]);
+    top_p = __uint_as_float(st.dev_params[1]);
+    min_p = __uint_as_float(st.dev_params[2]);
+    penalty = __uint_as_float(st.dev_params[3]);
+    penalty_window = (int)st.dev_params[4];
+}
 
 __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
     z += 0x9E3779B97F4A7C15ull;
@@ -257,7 +271,8 @@ __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
 }
 __device__ __forceinline__ float row_uniform(const SampleState& st, int r) {
     if (st.uniforms != nullptr) return st.uniforms[r];
-    const unsigned long long z = mix64(mix64(mix64(st.seed) ^ (unsigned long long)st.requests[r]) ^ (unsigned long long)st.steps[r]);
+    const unsigned long long seed = st.dev_params ? (((unsigned long long)st.dev_params[7] << 32) | st.dev_params[6]) : st.seed;
+    const unsigned long long z = mix64(mix64(mix64(seed) ^ (unsigned long long)st.requests[r]) ^ (unsigned long long)st.steps[r]);
     return (float)(z >> 40) * (1.0f / 16777216.0f);
 }
 // One thread: the row's result, and what the next step of the row starts from.
@@ -445,6 +460,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const SampleState st,
     __shared__ int warp_counts[32];
     __shared__ int bad;
     extern __shared__ __align__(16) unsigned warp_hists[];      // one histogram of 256 digits per warp
+    load_device_params(st, temperature, top_p, min_p, penalty, penalty_window);
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * vocab;
     float* probs = scratch + (size_t)r * 3 * vocab;
@@ -718,6 +734,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int vocab, int per, cons
     __shared__ __align__(8) int misc[8];
     __shared__ int warp_counts[32];
     __shared__ int bad;
+    load_device_params(st, temperature, top_p, min_p, penalty, penalty_window);
     const int rank = (int)ptx::cluster_rank();
     const int r = blockIdx.y;
     const float* row = logits + (size_t)r * vocab;
@@ -917,7 +934,8 @@ extern "C" int mdma_sample(const float* logits, int n_rows, int vocab, int* hist
                            int* history_len, int history_stride, const float* uniforms,
                            const int* requests, int* steps, unsigned long long seed, int advance,
                            float temperature, float top_p, float min_p, float penalty, int penalty_window,
-                           float* probs_scratch, long scratch_words, int* tokens, int* flags, int impl, cudaStream_t stream) {
+                           float* probs_scratch, long scratch_words, int* tokens, int* flags, int impl,
+                           const unsigned* dev_params, cudaStream_t stream) {
     MDMA_REQUIRE(vocab > 0 && n_rows >= 0, "sample: bad sizes");
     MDMA_REQUIRE(probs_scratch != nullptr, "sample: scratch is required");
     MDMA_REQUIRE(uniforms != nullptr || (requests != nullptr && steps != nullptr),
@@ -927,6 +945,7 @@ extern "C" int mdma_sample(const float* logits, int n_rows, int vocab, int* hist
     SampleState st;
     st.history = history; st.history_len = history_len; st.history_stride = history_stride;
     st.uniforms = uniforms; st.requests = requests; st.steps = steps; st.seed = seed; st.advance = advance;
+    st.dev_params = dev_params;
     MDMA_REQUIRE(scratch_words >= 3l * n_rows * vocab, "sample: %ld words of scratch needed, %ld given", 3l * n_rows * vocab, scratch_words);
     MDMA_REQUIRE(penalty > 0.f, "sample: repetition penalty must be positive");
     if (n_rows == 0) return 0;

@@ -66,9 +66,12 @@ def token_budget(prompt_len: int, max_tokens: int, max_context: int) -> tuple[in
 
 
 class Generator:
-    def __init__(self, engine, sampler, use_graphs: bool = True):
-        self.engine, self.sampler, self.use_graphs = engine, sampler, use_graphs
-        self._sessions: dict = {}
+    """`run_ahead`: how many decode steps are replayed back to back before the host reads their
+    tokens (a sequence that stops inside such a run has computed a few tokens for nothing)."""
+
+    def __init__(self, engine, sampler=None, use_graphs: bool = True, run_ahead: int = 8):
+        self.engine, self.use_graphs, self.run_ahead = engine, use_graphs, max(1, run_ahead)
+        self.sampler = sampler if sampler is not None else engine.sampler
 
     def plan_batches(self, sizes: Sequence[tuple[int, int]]) -> list[list[int]]:
         """Cut request indices, in order, into batches the cache can hold at once."""
@@ -93,83 +96,104 @@ class Generator:
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 32,
                  params: Optional[SamplingParams] = None, stop_ids: Sequence[int] = (),
                  cancelled: Optional[Callable[[], bool]] = None,
-                 on_token: Optional[Callable[[int, int], None]] = None) -> list[Output]:
+                 on_token: Optional[Callable[[int, int], None]] = None,
+                 use_graphs: Optional[bool] = None) -> list[Output]:
         params = params or SamplingParams.greedy()
         params.validate()
         stop = frozenset(int(s) for s in stop_ids)
         if params.repetition_penalty != 1.0 and hasattr(self.sampler, "ensure_history"):
-            if self.sampler.ensure_history(params.repetition_window):
-                self._sessions.clear()          # their graphs hold the old history buffers
+            self.sampler.ensure_history(params.repetition_window)       # refuses a window it has no room for
         budgets = [token_budget(len(p), max_tokens, self.engine.max_context) for p in prompts]
         outputs = [Output(list(p)) for p in prompts]
         sizes = [(len(p), b) for p, (b, _) in zip(prompts, budgets)]
+        graphs = self.use_graphs if use_graphs is None else use_graphs
         for batch in self.plan_batches(sizes):
-            self._run_batch(batch, prompts, budgets, outputs, params, stop, cancelled, on_token)
+            self._run_batch(batch, prompts, budgets, outputs, params, stop, cancelled, on_token, graphs)
         return outputs
 
-    def _run_batch(self, batch, prompts, budgets, outputs, params, stop, cancelled, on_token) -> None:
+    def _absorb(self, live, tokens, flags, outputs, stop, on_token) -> list:
+        """One step's tokens: append, or end the sequence.  Returns the sequences that go on."""
+        survivors = []
+        for s, tok, bad in zip(live, tokens, flags):
+            out = outputs[s.request]
+            if s.slot < 0:                  # ended at an earlier step of the same run
+                continue
+            s.steps += 1
+            if bad:
+                out.finish_reason = FINISH_NONFINITE       # src/inference.rs:111-113
+            elif tok in stop:
+                out.finish_reason = FINISH_STOP            # not emitted: src/inference.rs:115-118
+            else:
+                out.tokens.append(tok)
+                if on_token is not None:
+                    on_token(s.request, tok)
+                if len(out.tokens) >= s.budget:            # the last token is not fed back
+                    out.finish_reason = FINISH_CONTEXT if s.context_limited else FINISH_LENGTH
+                else:
+                    s.next_token = tok
+                    survivors.append(s)
+                    continue
+            self.engine.release(s.slot)
+            s.slot = -1
+        return survivors
+
+    def _run_batch(self, batch, prompts, budgets, outputs, params, stop, cancelled, on_token, graphs) -> None:
         live = [_Live(r, self.engine.acquire(), budgets[r][0], budgets[r][1]) for r in batch]
         penalised = params.repetition_penalty != 1.0 and params.repetition_window > 0
         session = None
-        session_fresh = False          # whether the session's device buffers describe this batch
+        session_fresh = False          # whether the session's device buffers describe the live sequences
+
+        def histories_of(seqs):
+            if not penalised:
+                return None
+            return [outputs[s.request].prompt_tokens + outputs[s.request].tokens for s in seqs]
+
+        def cancel_all():
+            for s in live:
+                outputs[s.request].finish_reason = FINISH_CANCELLED
         try:
+            if cancelled is not None and cancelled():
+                cancel_all()
+                return
+            # all prompts of the batch in one step
             entries = [StepEntry(s.slot, list(prompts[s.request]), [len(prompts[s.request]) - 1]) for s in live]
-            first = True
+            logits = self.engine.step(entries)
+            tokens, flags = self.sampler.sample(logits, params, [s.request for s in live],
+                                                [s.steps for s in live], histories_of(live))
+            if hasattr(self.engine, "check_status"):
+                self.engine.check_status()
+            live = self._absorb(live, tokens, flags, outputs, stop, on_token)
+            if live and graphs and hasattr(self.engine, "decode_session"):
+                session = self.engine.decode_session()
+                if not session.graph_safe:
+                    session = None
             while live:
                 if cancelled is not None and cancelled():
-                    for s in live:
-                        outputs[s.request].finish_reason = FINISH_CANCELLED
+                    cancel_all()
                     break
-                histories = None
-                if penalised:
-                    histories = [outputs[s.request].prompt_tokens + outputs[s.request].tokens for s in live]
-                if first or session is None:
-                    logits = self.engine.step(entries)
-                    tokens, flags = self.sampler.sample(logits, params, [s.request for s in live],
-                                                        [s.steps for s in live], histories)
-                else:
-                    # decode: this step's input tokens go up from the host, the step is replayed
-                    # as a graph, the selected tokens come back
-                    slots_now = [s.slot for s in live]
-                    if session.slots == slots_now and session_fresh:
-                        session.feed([s.next_token for s in live])
-                        session.steps_done = [s.steps for s in live]
-                    else:
-                        session.start(slots_now, [s.next_token for s in live],
-                                      [s.request for s in live], [s.steps for s in live])
-                        session_fresh = True
-                    session.step_async(histories)
-                    tokens, flags = session.read_tokens()
-                survivors = []
-                for s, tok, bad in zip(live, tokens, flags):
-                    out = outputs[s.request]
-                    s.steps += 1
-                    if bad:
-                        out.finish_reason = FINISH_NONFINITE       # src/inference.rs:111-113
-                    elif tok in stop:
-                        out.finish_reason = FINISH_STOP            # not emitted: src/inference.rs:115-118
-                    else:
-                        out.tokens.append(tok)
-                        if on_token is not None:
-                            on_token(s.request, tok)
-                        if len(out.tokens) >= s.budget:            # the last token is not fed back
-                            out.finish_reason = FINISH_CONTEXT if s.context_limited else FINISH_LENGTH
-                        else:
-                            s.next_token = tok
-                            survivors.append(s)
-                            continue
-                    self.engine.release(s.slot)
-                    s.slot = -1
-                live = survivors
-                if first and live and self.use_graphs and hasattr(self.engine, "decode_session"):
-                    session = self._sessions.get(params)
-                    if session is None:
-                        session = self._sessions[params] = self.engine.decode_session(self.sampler, params)
-                    if not session.graph_safe:
-                        session = None
-                first = False
                 if session is None:
                     entries = [StepEntry(s.slot, [s.next_token], [0]) for s in live]
+                    logits = self.engine.step(entries)
+                    tokens, flags = self.sampler.sample(logits, params, [s.request for s in live],
+                                                        [s.steps for s in live], histories_of(live))
+                    if hasattr(self.engine, "check_status"):
+                        self.engine.check_status()
+                    live = self._absorb(live, tokens, flags, outputs, stop, on_token)
+                    continue
+                # decode: a run of steps replayed as graphs; the tokens a step selects are the next
+                # step's inputs on the device, the host reads the run's tokens in one copy
+                slots_now = [s.slot for s in live]
+                if not (session_fresh and session.slots == slots_now):
+                    session.start(slots_now, [s.next_token for s in live], [s.request for s in live],
+                                  [s.steps for s in live], params)
+                    session_fresh = True
+                # no sequence runs past its own budget (a stop token may still end one inside the run)
+                n = min(self.run_ahead, min(s.budget - len(outputs[s.request].tokens) for s in live))
+                session.run(n, histories_of(live))
+                run = list(live)
+                for tokens, flags in session.read():
+                    self._absorb(run, tokens, flags, outputs, stop, on_token)
+                live = [s for s in run if s.slot >= 0]
         finally:
             for s in live:
                 if s.slot >= 0:
@@ -184,11 +208,9 @@ def generate(model_dir: str, prompts: Sequence[Sequence[int]], max_tokens: int =
              max_batch: int = 8, max_context: Optional[int] = None, use_graphs: bool = True,
              **engine_args) -> list[Output]:
     """One call from a model folder and token-id prompts to generated token ids."""
-    from ..sampling.sampler import DeviceSampler
     from .step import Engine
     engine = Engine(model_dir, dtype=dtype, max_batch=max_batch, max_context=max_context, **engine_args)
-    sampler = DeviceSampler(engine.vocab_size, engine.max_slots, engine.device)
     params = SamplingParams(temperature, top_p, min_p, repetition_penalty, repetition_window, seed)
     if stop_ids is None:
         stop_ids = engine.spec.stop_token_ids
-    return Generator(engine, sampler, use_graphs).generate(prompts, max_tokens, params, stop_ids)
+    return Generator(engine, use_graphs=use_graphs).generate(prompts, max_tokens, params, stop_ids)

@@ -74,11 +74,53 @@ class DecoderModel:
                 cols[name] = (max(c, old[0]) if old else c, kind)
         return cols
 
+    def device_tensor_bytes(self, align: int = 256) -> int:
+        """Bytes of the device tensors the parts derive at bind (each rounded up to `align`)."""
+        total = 0
+        for part in self.all_parts():
+            for shape, dtype in part.device_tensors().values():
+                n = 1
+                for d in shape:
+                    n *= int(d)
+                total += -(-n * torch.empty((), dtype=dtype).element_size() // align) * align
+        return total
+
     # ---- weights ---------------------------------------------------------
+    def lay_out_weights(self, expected: dict[str, TensorSpec], held_dtype, take) -> dict:
+        """Where every tensor lives: `take(shape, dtype)` hands out (zeroed) device memory, or None
+        when only sizes are wanted.  Tensors that a part wants as rows of one matrix (`fused_tensors`)
+        get one region, the pieces are views of its rows; the whole is returned under its own name.
+        `held_dtype(name, spec)` is the dtype a tensor is kept in."""
+        tensors: dict = {}
+        for part in self.all_parts():
+            for whole, locals_ in part.fused_tensors().items():
+                whole_name = part.spec.tensor_name(whole)
+                names = [part.spec.tensor_name(l) for l in locals_]
+                if whole_name in tensors or any(n in tensors for n in names):
+                    continue          # placed already (a part that runs at two places of the schedule)
+                specs = [expected[n] for n in names]
+                dtypes = {held_dtype(n, s) for n, s in zip(names, specs)}
+                if any(len(s.shape) != 2 or s.shape[1] != specs[0].shape[1] for s in specs) or len(dtypes) != 1:
+                    raise ValueError(f"{whole_name}: only matrices of one width and dtype can share a matrix")
+                rows = sum(s.shape[0] for s in specs)
+                t = take((rows, specs[0].shape[1]), dtypes.pop())
+                tensors[whole_name] = t
+                r = 0
+                for n, sp in zip(names, specs):
+                    tensors[n] = None if t is None else t[r:r + sp.shape[0]]
+                    r += sp.shape[0]
+        for name, ts in expected.items():
+            if name not in tensors:
+                tensors[name] = take(ts.shape, held_dtype(name, ts))
+        return tensors
+
     def bind(self, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         for part in self.all_parts():
             local = {l: tensors[part.spec.tensor_name(l)] for l in part.tensor_specs()}
+            for whole in part.fused_tensors():
+                if part.spec.tensor_name(whole) in tensors:
+                    local[whole] = tensors[part.spec.tensor_name(whole)]
             part.bind(local, rt)
 
     def resident_bytes(self) -> int:
@@ -103,11 +145,16 @@ class DecoderModel:
                                              owns_cache=entry.cache is None)
         if ctx.rt.gemm == "tensor":
             from .. import ops_tensor
-            ops_tensor.flush_pending(x.device)
-        if ctx.n_want:
-            h = ctx.buf("h_rows", self.spec.hidden_size)
-            self.final_norm.forward(ctx, x, h, rows=ctx.want_rows, n_rows=ctx.n_want)
-            self.head.forward(ctx, h, logits, ctx.n_want)
+            ops_tensor.flush_pending(x.device, ctx.rt.tc)
+        if logits is not None and ctx.n_want:
+            self.logits_of(ctx, ctx.want_rows, ctx.n_want, logits)
+
+    def logits_of(self, ctx, rows: torch.Tensor, n_rows: int, logits: torch.Tensor) -> None:
+        """After `forward`: logits [n_rows, vocab] of the pass's rows `rows` (device indices)."""
+        x = ctx.buf("x", self.spec.hidden_size, torch.float32)
+        h = ctx.buf("h_rows", self.spec.hidden_size)
+        self.final_norm.forward(ctx, x, h, rows=rows, n_rows=n_rows)
+        self.head.forward(ctx, h, logits, n_rows)
 
 
 def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:

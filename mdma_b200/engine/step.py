@@ -25,7 +25,8 @@ import torch
 from ..cache import SequenceCache
 from ..config import load_config
 from ..parts.base import Runtime
-from ..weights import load_tensors, random_tensors, resident_dtype
+from ..weights import load_tensors, random_tensor, resident_dtype, stored_dtypes
+from .arena import Carver
 from .model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
@@ -73,42 +74,82 @@ class StepContext:
         return t
 
 
-def memory_plan(model: DecoderModel, expected, dtype, max_tokens, max_slots, max_context, page_size,
-                chunk_tokens, stored: Optional[dict] = None) -> dict:
-    """Bytes the engine will hold, from sizes alone (src/model/planning.rs:55-125).  `stored` gives
-    the dtype each tensor has in the file (vectors stay as stored); without it bfloat16 is assumed."""
-    elem = 4 if dtype == torch.float32 else 2
-    weights = 0
-    for name, ts in expected.items():
-        n = int(np.prod(ts.shape))
-        held = resident_dtype(ts, (stored or {}).get(name, torch.bfloat16), dtype)
-        weights += n * torch.empty((), dtype=held).element_size()
-    cache = SequenceCache(model.kv_needs(), model.state_needs(), max_tokens, max_slots, max_context, dtype,
-                          "meta", page_size, allocate=False)
-    ws = sum(chunk_tokens * cols * (4 if kind == "f32" else elem)
-             for cols, kind in model.workspace_columns().values())
-    return {"weights_bytes": weights, "cache_bytes": cache.bytes, "workspace_bytes": ws,
-            "total_bytes": weights + cache.bytes + ws, "cache_pages": cache.n_pages,
-            "page_size": page_size, "slots": max_slots, "chunk_tokens": chunk_tokens}
+class Layout:
+    """Everything an engine keeps on the device, as views of its arena (None when only planned)."""
+    pass
+
+
+def lay_out(model: DecoderModel, carver: Carver, *, dtype, device, sms: int, max_tokens: int, max_slots: int,
+            max_context: int, page_size: int, chunk_tokens: int, logit_rows: int, history_cap: int,
+            run_ahead: int = 8, stored: Optional[dict] = None) -> Layout:
+    """Carve the engine's memory, in a fixed order: weights, cache, workspace, logits, step
+    metadata, sampler, kernel scratch, tables the parts derive.  Run with a planning carver this
+    is the memory plan (src/model/planning.rs:55-125); run over the arena it is the allocation."""
+    from ..sampling.sampler import DeviceSampler
+    lay = Layout()
+    expected = model.expected_tensors()
+
+    def held(name, ts):
+        return resident_dtype(ts, (stored or {}).get(name, torch.bfloat16), dtype)
+    lay.tensors = model.lay_out_weights(expected, held, carver.taker("weights"))
+    lay.cache = SequenceCache(model.kv_needs(), model.state_needs(), max_tokens, max_slots, max_context, dtype,
+                              device, page_size, alloc=carver.taker("cache"))
+    lay.workspace = {}
+    for name, (cols, kind) in model.workspace_columns().items():
+        dt = torch.float32 if kind == "f32" else dtype
+        lay.workspace[name] = carver.take("workspace", (chunk_tokens, cols), dt)
+    lay.logits = carver.take("logits", (logit_rows, model.spec.vocab_size), torch.float32)
+    lay.meta_cap = 6 * chunk_tokens + 4 * max_slots + logit_rows + 16
+    lay.meta_dev = carver.take("metadata", (lay.meta_cap,), torch.int32)
+    # the replayed decode step reads its inputs from here: ids, positions (twice), slots, 0..cap
+    lay.decode = {name: carver.take("metadata", (max_slots + (1 if name == "arange" else 0),), torch.int32)
+                  for name in ("ids", "tok_pos", "seq_slot", "seq_pos0", "arange")}
+    lay.sampler = DeviceSampler(model.spec.vocab_size, max_slots, device, history_cap, alloc=carver.taker("sampler"))
+    # the result words (tokens, flags, status) of the last `run_ahead` replayed decode steps
+    lay.token_ring = carver.take("sampler", (max(1, run_ahead), 2 * max_slots + 4), torch.int32)
+    lay.ring_counter = carver.take("sampler", (1,), torch.int32)
+    shapes = []
+    for b in model.blocks:
+        m = b.mixer
+        if all(hasattr(m, a) for a in ("n_heads", "n_kv_heads", "head_dim")):
+            shapes.append((m.n_heads, m.n_kv_heads, m.head_dim))
+    floats = 0
+    if dtype == torch.bfloat16:
+        from .. import ops_tensor
+        floats = ops_tensor.scratch_floats_bound(sms, chunk_tokens, max_slots, shapes)
+    lay.scratch_floats = floats
+    lay.tc_sk_flags = carver.take("kernel_scratch", (max(512, 4 * sms),), torch.int32)
+    lay.tc_scratch = carver.take("kernel_scratch", (max(floats, 1),), torch.float32)
+    lay.tables = carver.take("tables", (max(model.device_tensor_bytes(), 1),), torch.uint8)
+    return lay
+
+
+def _plan_dict(carver: Carver, cache: SequenceCache, page_size, max_slots, chunk_tokens, logit_rows) -> dict:
+    plan = {f"{k}_bytes": v for k, v in carver.by_category.items()}
+    plan.update(total_bytes=carver.offset, cache_pages=cache.n_pages, page_size=page_size, slots=max_slots,
+                chunk_tokens=chunk_tokens, logit_rows=logit_rows)
+    return plan
 
 
 def plan_only(model_dir: str, dtype="bfloat16", max_batch: int = 1, max_context: Optional[int] = None,
-              chunk_tokens: int = 8192, page_size: int = 64) -> dict:
-    """The memory plan of a model folder without touching a device or reading weights."""
+              chunk_tokens: int = 8192, page_size: int = 64, sms: int = 148, history_cap: int = 256) -> dict:
+    """The memory plan of a model folder without touching a device or reading weights.  `sms`:
+    the multiprocessor count the kernels' scratch is sized for (a B200 has 148)."""
     arch, config = load_config(model_dir)
     spec = arch.describe(config)
     model = DecoderModel(spec)
     ctx = int(max_context or spec.max_positions)
     max_tokens = max_batch * (-(-ctx // page_size)) * page_size
-    stored = {}
     try:
-        from ..weights import open_model_files
-        for sf in open_model_files(model_dir):
-            stored.update({n: e.dtype for n, e in sf.entries.items()})
+        stored = stored_dtypes(model_dir)
     except Exception:
         stored = None                       # a folder without weights can still be planned
-    return memory_plan(model, model.expected_tensors(), _DTYPES[dtype], max_tokens, max_batch, ctx,
-                       page_size, max(1, min(chunk_tokens, max_tokens)), stored)
+    chunk = max(1, min(chunk_tokens, max_tokens))
+    carver = Carver()
+    lay = lay_out(model, carver, dtype=_DTYPES[dtype], device="meta", sms=sms, max_tokens=max_tokens,
+                  max_slots=max_batch, max_context=ctx, page_size=page_size, chunk_tokens=chunk,
+                  logit_rows=max_batch, history_cap=history_cap, stored=stored)
+    return _plan_dict(carver, lay.cache, page_size, max_batch, chunk, max_batch)
 
 
 class Engine:
@@ -116,7 +157,13 @@ class Engine:
                  seed: Optional[int] = None, dtype="bfloat16", max_tokens: Optional[int] = None,
                  max_batch: int = 8, max_context: Optional[int] = None, chunk_tokens: int = 8192,
                  device="cuda:0", reserve_mib: int = 256, kernels: str = "auto", page_size: int = 64,
-                 vram_bytes: Optional[int] = None, context_hint: Optional[int] = None):
+                 vram_bytes: Optional[int] = None, context_hint: Optional[int] = None,
+                 logit_rows: Optional[int] = None, history_cap: int = 256, init_std: Optional[float] = None,
+                 run_ahead: int = 8):
+        """`logit_rows`: the most places one step may want logits at (default: one per sequence slot);
+        `history_cap`: the longest repetition window the sampler keeps room for; `run_ahead`: how many
+        replayed decode steps may run before the host reads their tokens; `init_std`: the standard
+        deviation of seeded random matrices (default 0.02)."""
         if dtype not in _DTYPES:
             raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
         self.dtype = _DTYPES[dtype]
@@ -127,6 +174,8 @@ class Engine:
             raise RuntimeError("no CUDA device is available; the engine has no CPU path")
         if (model_dir is None) == (config is None):
             raise ValueError("give either a model folder or a configuration dictionary (with a seed)")
+        if model_dir is None and seed is None:
+            raise ValueError("random weights need a seed")
         self.arch, self.config = load_config(model_dir if model_dir is not None else config)
         self.spec = self.arch.describe(self.config)
         self.model = DecoderModel(self.spec)
@@ -145,6 +194,7 @@ class Engine:
             self.max_slots = max(1, min(-(-max_tokens // page_size), 4096))
         self.max_tokens = -(-int(max_tokens) // page_size) * page_size
         self.chunk_tokens = max(1, min(int(chunk_tokens), self.max_tokens))
+        self.logit_rows = max(1, int(logit_rows if logit_rows is not None else self.max_slots))
 
         if kernels == "auto":
             kernels = "tensor" if self.dtype == torch.bfloat16 else "plain"
@@ -155,14 +205,29 @@ class Engine:
         self.rt = Runtime(self.dtype, self.device,
                           gemm="tensor" if kernels == "tensor" else "simt",
                           attention="fast" if kernels == "tensor" else "simple")
+        # sizes the kernels cannot take are refused here, before anything is read or allocated
+        # (the reference's backend limit at admission: src/model/arch/llama/preflight.rs:35-42)
+        for part in self.model.all_parts():
+            check = getattr(part, "check_limits", None)
+            if check is not None:
+                check(self.rt)
 
         # ---- plan, then allocate ----------------------------------------
-        expected = self.model.expected_tensors()
-        stored = None
-        if model_dir is not None:
-            from ..weights import open_model_files
-            stored = {n: e.dtype for sf in open_model_files(model_dir) for n, e in sf.entries.items()}
-        self.plan = self._plan(expected, stored)
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        stored = stored_dtypes(model_dir) if model_dir is not None else None
+        if stored is not None:          # the folder's headers are checked before the device is touched
+            from ..weights import check_entries, open_model_files
+            entries = {}
+            for sf in open_model_files(model_dir):
+                entries.update(sf.entries)
+            check_entries(entries, self.model.expected_tensors(), where=model_dir)
+        sizes = dict(dtype=self.dtype, device=self.device, sms=sms, max_tokens=self.max_tokens,
+                     max_slots=self.max_slots, max_context=self.max_context, page_size=page_size,
+                     chunk_tokens=self.chunk_tokens, logit_rows=self.logit_rows, history_cap=history_cap,
+                     run_ahead=run_ahead, stored=stored)
+        planner = Carver()
+        planned = lay_out(self.model, planner, **sizes)
+        self.plan = _plan_dict(planner, planned.cache, page_size, self.max_slots, self.chunk_tokens, self.logit_rows)
         free, _total = torch.cuda.mem_get_info(self.device)
         if vram_bytes is not None:
             free = min(free, int(vram_bytes))
@@ -171,63 +236,105 @@ class Engine:
             raise MemoryBudgetError(need, free, self.plan)
 
         with torch.cuda.device(self.device):
+            self.arena = torch.zeros(self.plan["total_bytes"], dtype=torch.uint8, device=self.device)
+            carver = Carver(self.arena)
+            lay = lay_out(self.model, carver, **sizes)
+            assert carver.offset == planner.offset and carver.by_category == planner.by_category
+            self._held = dict(carver.by_category)
+            expected = self.model.expected_tensors()
             if model_dir is not None:
-                tensors = load_tensors(model_dir, expected, self.dtype, self.device)
+                load_tensors(model_dir, expected, self.dtype, self.device, into=lay.tensors)
             else:
-                if seed is None:
-                    raise ValueError("random weights need a seed")
-                tensors = {}
+                from ..weights.random_init import INIT_STD, quantile_table
+                table = torch.from_numpy(quantile_table()).to(self.device)
                 for name, ts in expected.items():
-                    stored = torch.float32 if self.dtype == torch.float32 else torch.bfloat16
-                    tensors.update(random_tensors({name: ts}, seed,
-                                                  resident_dtype(ts, stored, self.dtype), self.device))
-            self.model.bind(tensors, self.rt)
-            del tensors
-            self.cache = SequenceCache(self.model.kv_needs(), self.model.state_needs(), self.max_tokens,
-                                       self.max_slots, self.max_context, self.dtype, self.device, page_size)
-            self.workspace = {}
-            for name, (cols, kind) in self.model.workspace_columns().items():
-                dt = torch.float32 if kind == "f32" else self.dtype
-                self.workspace[name] = torch.empty((self.chunk_tokens, cols), dtype=dt, device=self.device)
+                    random_tensor(name, ts, seed, lay.tensors[name].dtype, out=lay.tensors[name], table=table,
+                                  std=INIT_STD if init_std is None else init_std)
+                torch.cuda.synchronize(self.device)
+                del table
+            self.sampler = lay.sampler
+            if self.rt.gemm == "tensor":
+                from .. import ops_tensor
+                # the kernels' status word lies beside the sampler's tokens: one copy brings both to the host
+                self.rt.tc = ops_tensor.TensorState(self.device, lay.scratch_floats, sms=sms, status=self.sampler.extra,
+                                                    sk_flags=lay.tc_sk_flags, scratch=lay.tc_scratch)
+            tables = Carver(lay.tables)
+            self.rt.alloc = tables.taker("tables")
+            self.model.bind(lay.tensors, self.rt)
+            self.cache = lay.cache
+            self.workspace = lay.workspace
+            self.logits = lay.logits
+            self.decode_buffers = lay.decode
+            self.token_ring, self.ring_counter = lay.token_ring, lay.ring_counter
+            self.decode_buffers["arange"].copy_(torch.arange(self.max_slots + 1, dtype=torch.int32))
             # step metadata goes up in one copy from pinned memory; two host buffers
             # take turns so that one can be filled while the other's copy is in flight
-            self._meta_cap = 6 * self.chunk_tokens + 4 * self.max_slots + 16
+            self._meta_cap = lay.meta_cap
             self._meta_host = [torch.empty(self._meta_cap, dtype=torch.int32).pin_memory() for _ in range(2)]
             self._meta_event = [torch.cuda.Event() for _ in range(2)]
             self._meta_turn = 0
-            self._meta_dev = torch.empty(self._meta_cap, dtype=torch.int32, device=self.device)
+            self._meta_dev = lay.meta_dev
+            self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+            self._status_event = None
         self.ctx = StepContext(self.rt, self.workspace)
         self.forward_passes = 0
+        self.h2d_bytes = self.d2h_bytes = 0     # bytes of step inputs copied up / results copied down so far
+        self._session = None
+        self._generator = None
 
     # ---- planning ----------------------------------------------------------
-    def _plan(self, expected, stored=None) -> dict:
-        return memory_plan(self.model, expected, self.dtype, self.max_tokens, self.max_slots,
-                           self.max_context, self.page_size, self.chunk_tokens, stored)
+    def memory_plan(self) -> dict:
+        return dict(self.plan)
 
     def held_bytes(self) -> dict:
-        """Bytes actually resident, in the plan's categories."""
-        cache = sum(g.k.numel() * g.k.element_size() * 2 + g.table_host.nbytes for g in self.cache.groups)
-        cache += sum(t.numel() * t.element_size() for t in self.cache.states.values())
-        ws = sum(t.numel() * t.element_size() for t in self.workspace.values())
-        return {"weights_bytes": self.model.resident_bytes(), "cache_bytes": cache, "workspace_bytes": ws}
+        """Bytes actually resident, in the plan's categories: the arena is the only device memory
+        the engine keeps, carved by the function that made the plan."""
+        held = {f"{k}_bytes": v for k, v in self._held.items()}
+        held["total_bytes"] = self.arena.numel()
+        return held
+
+    # ---- kernel status -------------------------------------------------------
+    def check_status(self, sync: bool = True) -> None:
+        """Raise `KernelError` if a tensor-core kernel gave up on a bounded wait since the last
+        check (its output is then not valid).  `sync=False` looks only at the copy of the status
+        word that the last `step` left on the host, if it has arrived."""
+        tc = self.rt.tc
+        if tc is None:
+            return
+        if sync:
+            self._status_host.copy_(tc.status, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        elif self._status_event is None or not self._status_event.query():
+            return
+        self._status_event = None
+        self.raise_on_status(int(self._status_host[0]))
+
+    def raise_on_status(self, word: int) -> None:
+        if word != 0:
+            from ..ops import KernelError
+            self.rt.tc.clear()
+            raise KernelError(f"a tensor-core kernel ran into its wait limit (status {word}); "
+                              "the results of this step are not valid")
 
     def generate(self, prompts, max_tokens: int = 32, temperature: float = 0.0, seed: int = 0,
                  stop_ids=None, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
                  repetition_window: int = 64, use_graphs: bool = True):
         """Generate from token-id prompts on this engine; see `mdma_b200.generate`."""
         from ..sampling.params import SamplingParams
-        from ..sampling.sampler import DeviceSampler
         from .generate import Generator
-        if getattr(self, "_generator", None) is None:
-            self._generator = Generator(self, DeviceSampler(self.vocab_size, self.max_slots, self.device), use_graphs)
+        if self._generator is None:
+            self._generator = Generator(self)
         params = SamplingParams(temperature, top_p, min_p, repetition_penalty, repetition_window, seed)
         stop = self.spec.stop_token_ids if stop_ids is None else stop_ids
-        return self._generator.generate(prompts, max_tokens, params, stop)
+        return self._generator.generate(prompts, max_tokens, params, stop, use_graphs=use_graphs)
 
-    def decode_session(self, sampler, params=None):
-        """A `DecodeSession` over this engine (decode steps replayed as CUDA graphs)."""
+    def decode_session(self):
+        """The engine's `DecodeSession` (decode steps replayed as CUDA graphs).  There is one:
+        its graphs serve every request, whatever its sampling options."""
         from .graphs import DecodeSession
-        return DecodeSession(self, sampler, params)
+        if self._session is None:
+            self._session = DecodeSession(self)
+        return self._session
 
     # ---- sequences ---------------------------------------------------------
     def acquire(self) -> int:
@@ -267,25 +374,33 @@ class Engine:
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"wanted place {w} is outside the {n} tokens of slot {e.slot}")
+            if len({int(w) for w in e.want}) != len(e.want):
+                raise StepError(f"a wanted place of slot {e.slot} is listed twice")
+        n_want = sum(len(e.want) for e in entries)
+        if n_want > self.logit_rows:
+            raise StepError(f"the step wants logits at {n_want} places, the engine has room for "
+                            f"{self.logit_rows} (Engine(logit_rows=...))")
         why = self.cache.can_extend({e.slot: len(e.tokens) for e in entries})
         if why:
             raise StepError(why)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens; returns float32 logits [sum of wants, vocab] on the device,
-        in the order of the entries and of each entry's `want`."""
+        in the order of the entries and of each entry's `want`.  The result is a view of the
+        engine's own logits buffer: it holds until the next step."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
+        self.check_status(sync=False)
         ext = {e.slot: len(e.tokens) for e in entries}
         self.cache.extend(ext)
         n_want = sum(len(e.want) for e in entries)
-        logits = torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device)
+        logits = self.logits[:n_want]
         # where each wanted row goes in the result: entries' order, then want's order
         out_row = {}
         r = 0
         for i, e in enumerate(entries):
             for w in e.want:
-                out_row.setdefault((i, int(w)), []).append(r)
+                out_row[(i, int(w))] = r
                 r += 1
         # cut the flat token list into passes of at most chunk_tokens tokens
         cursor = [0] * len(entries)
@@ -306,11 +421,17 @@ class Engine:
             for i, start, take in pieces:
                 cursor[i] = start + take
         self.cache.commit(ext)
+        if self.rt.tc is not None:
+            # the kernels' status word follows the step to the host; the next step (or
+            # `check_status`) looks at it, so a wait that ran out does not pass unnoticed
+            self._status_host.copy_(self.rt.tc.status, non_blocking=True)
+            self._status_event = torch.cuda.Event()
+            self._status_event.record()
         return logits
 
     def _forward(self, entries, pieces, base, out_row, logits) -> None:
         ids, tok_seq, tok_pos, seq_slot, seq_start, seq_pos0 = [], [], [], [], [0], []
-        want_rows, dest_rows = [], []
+        wanted = []                     # (row of the result, row of this pass)
         max_new = max_len = 0
         n_rows = 0
         for s, (i, start, take) in enumerate(pieces):
@@ -326,27 +447,23 @@ class Engine:
             seq_start.append(n_rows)
             max_new = max(max_new, take)
             max_len = max(max_len, pos0 + take)
-            for j in sorted({int(w) for w in e.want}):
-                if start <= j < start + take:
-                    for dest in out_row.get((i, j), ()):
-                        want_rows.append(first_row + j - start)
-                        dest_rows.append(dest)
-        if want_rows:          # keep the result rows in the order of the entries and of each `want`
-            order = sorted(range(len(dest_rows)), key=dest_rows.__getitem__)
-            want_rows = [want_rows[k] for k in order]
-            dest_rows = [dest_rows[k] for k in order]
+            for w in e.want:
+                if start <= int(w) < start + take:
+                    wanted.append((out_row[(i, int(w))], first_row + int(w) - start))
+        wanted.sort()                   # in the order of the result rows
+        want_rows = [row for _, row in wanted]
         ids, tok_seq, tok_pos = np.concatenate(ids), np.concatenate(tok_seq), np.concatenate(tok_pos)
         T, B, W = len(ids), len(pieces), len(want_rows)
         fields = [ids, tok_seq, tok_pos, seq_slot, seq_start, seq_pos0, want_rows]
-        flat = np.concatenate([np.asarray(f, dtype=np.int32) for f in fields]) if T else None
+        flat = np.concatenate([np.asarray(f, dtype=np.int32) for f in fields])
         n = flat.size
-        if n > self._meta_cap:
-            raise StepError("too many wanted places for one pass")
+        assert n <= self._meta_cap
         turn = self._meta_turn = self._meta_turn ^ 1
         self._meta_event[turn].synchronize()
         self._meta_host[turn][:n].copy_(torch.from_numpy(flat))
         self._meta_dev[:n].copy_(self._meta_host[turn][:n], non_blocking=True)
         self._meta_event[turn].record()
+        self.h2d_bytes += 4 * n
         ctx = self.ctx
         off = 0
         views = []
@@ -356,17 +473,19 @@ class Engine:
         (ctx.ids, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot, ctx.seq_start, ctx.seq_pos0, ctx.want_rows) = views
         ctx.n_tokens, ctx.n_seqs, ctx.n_want = T, B, W
         ctx.max_new, ctx.max_len = max_new, max_len
+        ctx.decode_only = False
         ctx.host_seq_new = [take for _, _, take in pieces]
         ctx.host_seq_pos0 = list(seq_pos0)
         ctx.host_seq_slot = list(seq_slot)
-        contiguous = dest_rows == list(range(dest_rows[0], dest_rows[0] + W)) if W else True
-        if W and contiguous:
-            out = logits[dest_rows[0]:dest_rows[0] + W]
-            self.model.forward(ctx, self.cache, out)
-        elif W:
-            tmp = torch.empty((W, self.vocab_size), dtype=torch.float32, device=self.device)
-            self.model.forward(ctx, self.cache, tmp)
-            logits.index_copy_(0, torch.as_tensor(dest_rows, device=self.device), tmp)
-        else:
-            self.model.forward(ctx, self.cache, None)
+        self.model.forward(ctx, self.cache, None)
+        # logits of the wanted rows, written where they belong: one head call per run of result
+        # rows that follow one another (one run, unless a `want` list is out of order across a cut)
+        k = 0
+        while k < W:
+            j = k + 1
+            while j < W and wanted[j][0] == wanted[j - 1][0] + 1:
+                j += 1
+            dest0 = wanted[k][0]
+            self.model.logits_of(ctx, ctx.want_rows[k:j], j - k, logits[dest0:dest0 + (j - k)])
+            k = j
         self.forward_passes += 1

@@ -69,6 +69,15 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> Non
           _i(n), _i(table.shape[1]), _i(table.shape[0]), _stream())
 
 
+def fill_normal(out: torch.Tensor, key: int, table: torch.Tensor, std: float) -> None:
+    """out.flat[i] = std * (a normal quantile picked by a hash of (key, i)); the host side of the same
+    arithmetic is `weights.random_init.normal_values`.  `table`: 65,537 float quantiles on the device."""
+    _need_cuda(out, table)
+    assert out.is_contiguous() and table.dtype == torch.float32 and table.numel() == 65537
+    _call("core", "mdma_fill_normal", _ptr(out), _i(dtype_code(out.dtype)), ctypes.c_long(out.numel()),
+          ctypes.c_ulonglong(key & ((1 << 64) - 1)), _ptr(table), _f(std), _stream())
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
             partial: Optional[torch.Tensor] = None, splits: int = 0, split_stride: int = 0) -> None:
@@ -143,15 +152,24 @@ def attention_simple(q: torch.Tensor, n_tokens: int, k_cache, v_cache, tok_seq, 
 _argmax_scratch: dict = {}
 
 
+def argmax_scratch_words(n_rows: int, vocab: int) -> int:
+    return 3 * max(n_rows, 1) * (-(-vocab // 4096))
+
+
 def argmax(logits: torch.Tensor, tokens: torch.Tensor, flags: Optional[torch.Tensor] = None,
-           n_rows: Optional[int] = None) -> None:
+           n_rows: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> None:
     """tokens[r] = index of the largest logit of row r (the lowest index among equals);
-    flags[r] = 1 if the row holds a value that is not finite."""
-    _need_cuda(logits, tokens, flags)
+    flags[r] = 1 if the row holds a value that is not finite.  `scratch`: floats for the first
+    stage's partial results (`argmax_scratch_words`); without it a buffer of this module is used."""
+    _need_cuda(logits, tokens, flags, scratch)
     assert logits.dtype == torch.float32 and logits.is_contiguous() and tokens.dtype == torch.int32
     n = logits.shape[0] if n_rows is None else n_rows
-    need = 3 * max(n, 1) * (-(-logits.shape[1] // 4096))
-    scratch = _argmax_scratch.get(logits.device.index)
+    need = argmax_scratch_words(n, logits.shape[1])
+    if scratch is not None:
+        if scratch.numel() < need:
+            raise KernelError(f"argmax needs {need} words of scratch, {scratch.numel()} given")
+    else:
+        scratch = _argmax_scratch.get(logits.device.index)
     if scratch is None or scratch.numel() < need:
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("argmax scratch cannot grow during graph capture")
@@ -171,13 +189,17 @@ def sample(logits: torch.Tensor, uniforms: Optional[torch.Tensor], tokens: torch
            history: Optional[torch.Tensor] = None, history_len: Optional[torch.Tensor] = None,
            flags: Optional[torch.Tensor] = None, n_rows: Optional[int] = None, impl: int = 0,
            requests: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None, seed: int = 0,
-           advance: bool = False) -> None:
+           advance: bool = False, dev_params: Optional[torch.Tensor] = None) -> None:
     """One token per row of `logits`.  The uniform number of a row is `uniforms[r]`, or, without
     `uniforms`, made on the device from (seed, requests[r], steps[r]).  `history` [rows, cap] is a ring of
     recent token ids per row and `history_len` the count of tokens ever added to it.  `advance`: the
     kernel appends the selected token to the ring and adds one to `steps`.
-    `impl`: 0 picks (a cluster of eight blocks per row when the row fits), 1 one block per row, 2 the cluster."""
-    _need_cuda(logits, uniforms, tokens, probs_scratch, history, history_len, flags, requests, steps)
+    `impl`: 0 picks (a cluster of eight blocks per row when the row fits), 1 one block per row, 2 the cluster.
+    `dev_params` (eight 32-bit words on the device: temperature, top_p, min_p, penalty as floats, the
+    window, an unused word, the seed's low and high halves) replaces the options given by value, so that
+    a captured launch serves whatever the host writes there before a replay."""
+    _need_cuda(logits, uniforms, tokens, probs_scratch, history, history_len, flags, requests, steps, dev_params)
+    assert dev_params is None or (dev_params.dtype == torch.int32 and dev_params.numel() >= 8)
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     assert tokens.dtype == torch.int32 and (uniforms is None or uniforms.dtype == torch.float32)
     assert uniforms is not None or (requests is not None and steps is not None)
@@ -192,11 +214,16 @@ def sample(logits: torch.Tensor, uniforms: Optional[torch.Tensor], tokens: torch
           _ptr(history_len), _i(hstride), _ptr(uniforms), _ptr(requests), _ptr(steps),
           ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _i(int(advance)), _f(temperature), _f(top_p), _f(min_p),
           _f(penalty), _i(penalty_window), _ptr(probs_scratch), ctypes.c_long(probs_scratch.numel()), _ptr(tokens),
-          _ptr(flags), _i(impl), _stream())
+          _ptr(flags), _i(impl), _ptr(dev_params), _stream())
 
 
 def advance_decode(tokens: torch.Tensor, ids: torch.Tensor, tok_pos: torch.Tensor, seq_pos0: torch.Tensor,
-                   n: int) -> None:
-    """ids <- tokens, positions += 1: what a decode step leaves for the next one."""
-    _need_cuda(tokens, ids, tok_pos, seq_pos0)
-    _call("core", "mdma_advance_decode", _ptr(tokens), _ptr(ids), _ptr(tok_pos), _ptr(seq_pos0), _i(n), _stream())
+                   n: int, ring: Optional[torch.Tensor] = None, counter: Optional[torch.Tensor] = None) -> None:
+    """ids <- tokens, positions += 1: what a decode step leaves for the next one.  With `ring`
+    [rows, words] the first `words` integers at `tokens` (tokens, flags and what lies behind them in
+    the same buffer) are also kept in row counter % rows, and the counter moves on."""
+    _need_cuda(tokens, ids, tok_pos, seq_pos0, ring, counter)
+    words, rows = (ring.shape[1], ring.shape[0]) if ring is not None else (0, 0)
+    assert ring is None or (ring.dtype == torch.int32 and ring.is_contiguous() and counter.dtype == torch.int32)
+    _call("core", "mdma_advance_decode", _ptr(tokens), _ptr(ids), _ptr(tok_pos), _ptr(seq_pos0), _i(n),
+          _i(words), _ptr(ring), _i(rows), _ptr(counter), _stream())

@@ -13,29 +13,88 @@ from . import ops
 from .csrc import build as _build
 from .ops import KernelError, _call, _f, _i, _need_cuda, _ptr, _stream
 
-_state: dict = {}
 # MDMA_EVEN_SPLIT=0: the block-pair GEMM gives every pair whole tiles only (for comparisons).
 EVEN_SPLIT = os.environ.get("MDMA_EVEN_SPLIT", "1") != "0"
 
+PAIR_TOKENS = 128        # steps of more tokens than this run on the block-pair kernel
 
-def _device_state(device: torch.device) -> dict:
-    st = _state.get(device.index)
+
+def pair_scratch_floats(sms: int) -> int:
+    """Partial tiles of the block-pair kernel's even K-block split: one per block, two accumulators."""
+    return sms * 2 * 256 * 128
+
+
+def scratch_floats_bound(sms: int, max_tokens: int, max_seqs: int, attention_shapes=()) -> int:
+    """An upper bound of the scratch any step of up to `max_tokens` tokens in up to `max_seqs`
+    sequences needs, from sizes alone (an engine reserves this much once and never grows it).
+    K-split products keep splits x tokens x features floats with splits x tiles <= 2 x SMs, tiles of
+    128 features x up to 64 tokens (one per SM for 128 tokens); attention keeps tokens x heads x
+    splits x (head_dim + 2) floats.  `attention_shapes`: (heads, kv heads, head_dim) of each mixer."""
+    del max_seqs          # the bounds below hold for any number of sequences
+    need = 2 * sms * 128 * 64
+    if max_tokens > PAIR_TOKENS:
+        need = max(need, pair_scratch_floats(sms))
+    for heads, kv_heads, head_dim in attention_shapes:
+        group = max(1, heads // max(kv_heads, 1))
+        # Keys are split only while the grid is short of blocks (see `attention_splits`): decode has
+        # sequences x kv heads blocks < 2 x SMs and splits <= 3 x SMs / blocks + 1, so tokens x splits
+        # < 5 x SMs / kv heads; other steps have tokens <= blocks x tile tokens / kv heads and
+        # splits <= 2 x SMs / blocks + 1, so tokens x splits < 4 x SMs x tile tokens / kv heads.
+        tile_tokens = max(1, 64 // group)
+        need = max(need, 5 * sms * group * (head_dim + 2), 4 * sms * tile_tokens * group * (head_dim + 2))
+    return need
+
+
+class TensorState:
+    """What the tensor-core kernels share between launches on one device: a status word their
+    bounded waits set, the flags of the block-pair kernel's even split, scratch for partial sums,
+    and the record of a K-split product whose partial sums still wait to be added up.  An engine
+    owns one, carved from its arena and never reallocated (captured graphs hold its addresses);
+    kernels called without one (tests, tools) share a per-device default that may grow."""
+
+    def __init__(self, device: torch.device, scratch_floats: int, sms: Optional[int] = None,
+                 status: Optional[torch.Tensor] = None, sk_flags: Optional[torch.Tensor] = None,
+                 scratch: Optional[torch.Tensor] = None, growable: bool = False):
+        self.device = device
+        self.sms = sms if sms is not None else torch.cuda.get_device_properties(device).multi_processor_count
+        zeros = lambda n, dtype: torch.zeros(n, dtype=dtype, device=device)
+        self.status = status if status is not None else zeros(4, torch.int32)
+        self.sk_flags = sk_flags if sk_flags is not None else zeros(max(512, 4 * self.sms), torch.int32)
+        self.scratch = scratch if scratch is not None else zeros(max(scratch_floats, 1), torch.float32)
+        self.pending: Optional[Pending] = None
+        self.growable = growable
+
+    def need(self, floats: int, what: str) -> None:
+        if floats <= self.scratch.numel():
+            return
+        if not self.growable:
+            raise KernelError(f"{what} needs {floats} floats of scratch, the engine reserved {self.scratch.numel()}")
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError(f"{what}: scratch is too small and cannot grow during graph capture")
+        self.scratch = torch.empty(floats, dtype=torch.float32, device=self.device)
+
+    def clear(self) -> None:
+        """After a wait ran out: reset the status word and the flags a block pair may have left standing."""
+        self.status.zero_()
+        self.sk_flags.zero_()
+        self.pending = None
+
+
+_default: dict = {}
+
+
+def _device_state(device: torch.device) -> TensorState:
+    st = _default.get(device.index)
     if st is None:
-        st = {"pending": None,
-              "status": torch.zeros(4, dtype=torch.int32, device=device),
-              "sk_flags": torch.zeros(512, dtype=torch.int32, device=device),
-              "scratch": torch.empty(1 << 20, dtype=torch.float32, device=device),
-              "sms": torch.cuda.get_device_properties(device).multi_processor_count}
-        _state[device.index] = st
+        st = _default[device.index] = TensorState(device, 1 << 20, growable=True)
     return st
 
 
-def check_status(device: torch.device) -> None:
+def check_status(device: torch.device, st: Optional[TensorState] = None) -> None:
     """Raise if a tensor-core kernel gave up on a wait since the last check (synchronises)."""
-    st = _state.get(device.index)
-    if st is not None and int(st["status"][0].item()) != 0:
-        st["status"].zero_()
-        st["sk_flags"].zero_()          # a block pair that gave up may have left its flag standing
+    st = st or _default.get(device.index)
+    if st is not None and int(st.status[0].item()) != 0:
+        st.clear()
         raise KernelError("a tensor-core kernel ran into its wait limit; its output is not valid")
 
 
@@ -52,10 +111,8 @@ def gemm_plan(mode: int, n_tokens: int, n_features: int, k: int, sms: int) -> tu
 
 
 def reserve_scratch(device: torch.device, floats: int) -> None:
-    """Make the split-K scratch at least this large (call outside graph capture)."""
-    st = _device_state(device)
-    if st["scratch"].numel() < floats:
-        st["scratch"] = torch.empty(floats, dtype=torch.float32, device=device)
+    """Make the default state's scratch at least this large (call outside graph capture)."""
+    _device_state(device).need(floats, "reserve_scratch")
 
 
 class Pending:
@@ -68,38 +125,38 @@ class Pending:
         self.mode, self.splits, self.rows, self.cols = mode, splits, rows, cols
 
 
-def flush_pending(device: torch.device) -> None:
+def flush_pending(device: torch.device, st: Optional[TensorState] = None) -> None:
     """Finish a deferred K-split reduction with the plain reduce kernel."""
-    st = _state.get(device.index)
-    if st is None or st.get("pending") is None:
+    st = st or _default.get(device.index)
+    if st is None or st.pending is None:
         return
-    pend: Pending = st.pop("pending")
-    st["pending"] = None
+    pend, st.pending = st.pending, None
     out = pend.target
-    _call("tensor", "mdma_splitk_reduce", _i(pend.mode), _ptr(st["scratch"]), _i(pend.splits), _i(pend.rows),
+    _call("tensor", "mdma_splitk_reduce", _i(pend.mode), _ptr(st.scratch), _i(pend.splits), _i(pend.rows),
           _i(pend.cols), _ptr(out), _i(out.stride(0)), _i(int(out.dtype == torch.float32)), _stream())
 
 
-def take_pending(target: torch.Tensor, mode: int, rows: int):
+def take_pending(target: torch.Tensor, mode: int, rows: int, st: Optional[TensorState] = None):
     """If partial sums for exactly this target wait in the scratch, hand them to the caller, who
     will add them up itself: returns (scratch, splits, floats per split) or None."""
-    st = _state.get(target.device.index)
-    if st is None or st.get("pending") is None:
+    st = st or _default.get(target.device.index)
+    if st is None or st.pending is None:
         return None
-    pend: Pending = st["pending"]
+    pend = st.pending
     if (pend.target_ptr != target.data_ptr() or pend.mode != mode or pend.rows != rows
             or pend.cols != target.shape[1] or target.stride(0) != pend.cols):
         return None
-    st["pending"] = None
-    return st["scratch"], pend.splits, pend.rows * pend.cols
+    st.pending = None
+    return st.scratch, pend.splits, pend.rows * pend.cols
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GEMM_STORE,
          w2: Optional[torch.Tensor] = None, m: Optional[int] = None,
-         bn: Optional[int] = None, splits: Optional[int] = None, defer: bool = False) -> None:
+         bn: Optional[int] = None, splits: Optional[int] = None, defer: bool = False,
+         st: Optional[TensorState] = None) -> None:
     """out[:m] (=, +=) a[:m] @ w.T on the tensor cores; SwiGLU mode takes gate=w, up=w2.
     `defer`: if the product is split over K, leave its partial sums for the next kernel
-    (a norm or the rotary write) to add up; see `take_pending`."""
+    (a norm or the rotary write) to add up; see `take_pending`.  `st`: the engine's state."""
     _need_cuda(a, w, out, w2)
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("the tensor-core product takes bfloat16 operands")
@@ -109,27 +166,24 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
     assert a.shape[1] == K and out.shape[1] == N and out.shape[0] >= M and a.shape[0] >= M
     if out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError(f"output dtype {out.dtype} is not supported")
-    st = _device_state(a.device)
-    flush_pending(a.device)
+    st = st or _device_state(a.device)
+    flush_pending(a.device, st)
     if bn is None or splits is None:
-        pbn, psplits = gemm_plan(mode, M, N, K, st["sms"])
+        pbn, psplits = gemm_plan(mode, M, N, K, st.sms)
         bn = bn or pbn
         splits = splits or psplits
     need = splits * M * N if splits > 1 else 0
     if bn == 512:
-        need = 148 * 2 * 256 * 128          # partial tiles of the block-pair kernel's even K-block split
-    if need > st["scratch"].numel():
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("split-K scratch is too small and cannot grow during graph capture")
-        reserve_scratch(a.device, need)
+        need = pair_scratch_floats(st.sms)      # partial tiles of the block-pair kernel's even K-block split
+    st.need(need, "a K-split product")
     used = ctypes.c_int(1)
     _call("tensor", "mdma_gemm_tc", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), _ptr(out),
           _i(int(out.dtype == torch.float32)), _i(out.stride(0)), _i(M), _i(N), _i(K), _i(bn), _i(splits),
-          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]),
-          _i(int(defer)), ctypes.byref(used), _ptr(st["sk_flags"]) if EVEN_SPLIT else None, _stream(),
+          _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status),
+          _i(int(defer)), ctypes.byref(used), _ptr(st.sk_flags) if EVEN_SPLIT else None, _stream(),
           launches=1 if (splits == 1 or defer) else 2)
     if defer and used.value > 1:
-        st["pending"] = Pending(out, mode, used.value, M, N)
+        st.pending = Pending(out, mode, used.value, M, N)
 
 
 def attention_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
@@ -162,7 +216,8 @@ def attention_tc_supported(n_heads: int, n_kv_heads: int, head_dim: int, page_si
 
 
 def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-              window: int, scale: float, splits: Optional[int] = None, impl: Optional[str] = None) -> None:
+              window: int, scale: float, splits: Optional[int] = None, impl: Optional[str] = None,
+              st: Optional[TensorState] = None) -> None:
     """Causal grouped-query attention of the step's tokens over the paged cache (bfloat16).
     Steps that bring many tokens per sequence run on the tcgen05 kernel, single tokens on the
     decode kernel, what is between (or outside the tcgen05 kernel's limits) on the mma.sync kernel;
@@ -179,30 +234,26 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
             raise KernelError("the tensor-core attention takes bfloat16")
         assert qkv.stride(1) == 1 and out.is_contiguous() and out.shape[1] == n_heads * head_dim
         assert view.k.is_contiguous() and view.v.is_contiguous()
-        st = _device_state(qkv.device)
-        flush_pending(qkv.device)
+        st = st or _device_state(qkv.device)
+        flush_pending(qkv.device, st)
         _call("tensor", "mdma_attention_tc", _ptr(qkv), _i(qkv.stride(0)), _i(qkv.shape[0]), _ptr(view.k),
               _ptr(view.v), _i(view.k.shape[0]), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot),
               _ptr(view.page_table), _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens),
               _i(ctx.n_seqs), _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale),
-              _ptr(st["status"]), _stream())
+              _ptr(st.status), _stream())
         return
     _need_cuda(qkv, view.k, view.v, out, view.page_table)
     if qkv.dtype != torch.bfloat16 or view.k.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention takes bfloat16")
     assert qkv.stride(1) == 1 and out.is_contiguous() and out.shape[1] == n_heads * head_dim
-    st = _device_state(qkv.device)
-    flush_pending(qkv.device)
+    st = st or _device_state(qkv.device)
+    flush_pending(qkv.device, st)
     if splits is None:
-        splits = attention_splits(ctx.n_seqs, ctx.max_new, ctx.max_len, n_heads, n_kv_heads, st["sms"])
-    need = ctx.n_tokens * n_heads * splits * (head_dim + 2) if splits > 1 else 0
-    if need > st["scratch"].numel():
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("attention scratch is too small and cannot grow during graph capture")
-        reserve_scratch(qkv.device, need)
+        splits = attention_splits(ctx.n_seqs, ctx.max_new, ctx.max_len, n_heads, n_kv_heads, st.sms)
+    st.need(ctx.n_tokens * n_heads * splits * (head_dim + 2) if splits > 1 else 0, "attention over split keys")
     _call("tensor", "mdma_attention_mma_paged", _ptr(qkv), _i(qkv.stride(0)), _ptr(view.k), _ptr(view.v),
           _i(view.k.shape[0] if view.k.is_contiguous() and view.v.is_contiguous() else 0), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
           _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_tokens), _i(ctx.n_seqs),
           _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale), _i(splits),
-          _ptr(st["scratch"]), ctypes.c_long(st["scratch"].numel()), _ptr(st["status"]), _stream(),
+          _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status), _stream(),
           launches=2 if splits > 1 else 1)

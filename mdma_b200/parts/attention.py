@@ -53,6 +53,18 @@ class Attention(Part):
         specs["o_proj.weight"] = TensorSpec((self.hidden, self.q_width))
         return specs
 
+    MAX_HEAD_DIM = 256        # the plain attention kernel's limit (csrc/attention_simple.cu)
+
+    def check_limits(self, rt):
+        """Sizes no kernel of this library takes are refused when the engine is built, before
+        anything is loaded (src/model/arch/llama/preflight.rs:35-42)."""
+        if self.head_dim > self.MAX_HEAD_DIM:
+            raise ValueError(f"head_dim {self.head_dim} is beyond the attention kernels' limit of {self.MAX_HEAD_DIM}")
+
+    def fused_tensors(self):
+        # one product for q, k and v
+        return {} if self.shared_cache else {"qkv_proj.weight": ("q_proj.weight", "k_proj.weight", "v_proj.weight")}
+
     def kv_need(self):
         return KVNeed(self.n_kv_heads, self.head_dim, self.window)
 
@@ -68,8 +80,10 @@ class Attention(Part):
             self.position.bind({}, rt)      # a position part with tensors of its own is bound by the model
         if self.shared_cache:
             fused = tensors["q_proj.weight"]
+        elif "qkv_proj.weight" in tensors:
+            fused = tensors["qkv_proj.weight"]        # the loader filled the one matrix (see fused_tensors)
         else:
-            # one product for q, k and v: rows [q heads | k heads | v heads]
+            # bound by hand with three separate matrices: rows [q heads | k heads | v heads]
             fused = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
                                tensors["v_proj.weight"]], dim=0).contiguous()
         self._fast_ok = False
@@ -89,11 +103,11 @@ class Attention(Part):
         if self.rt.attention == "fast" and self._fast_ok:
             from .. import ops_tensor
             ops_tensor.attention(ctx, qkv, view, out, self.n_heads, self.n_kv_heads, self.head_dim,
-                                 self.window, self.scale)
+                                 self.window, self.scale, st=self.rt.tc)
         else:
             if self.rt.gemm == "tensor":
                 from .. import ops_tensor
-                ops_tensor.flush_pending(qkv.device)
+                ops_tensor.flush_pending(qkv.device, self.rt.tc)
             ops.attention_simple(qkv, n, view.k, view.v, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
                                  view.page_table, view.max_pages, view.page_size, out,
                                  self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)

@@ -33,6 +33,17 @@ class Runtime:
     device: torch.device
     gemm: str = "simt"                 # "simt" | "tensor" (tcgen05; bfloat16 only)
     attention: str = "simple"          # "simple" | "fast"
+    tc: object = None                  # the engine's `ops_tensor.TensorState` (None: a shared default)
+    alloc: object = None               # alloc(shape, dtype) for the device tensors a part derives at bind
+
+    def derived(self, host: torch.Tensor) -> torch.Tensor:
+        """A device copy of a small tensor a part computed on the host (a table of frequencies):
+        taken from the engine's arena when there is one (the part then names it in `device_tensors`)."""
+        if self.alloc is None:
+            return host.to(self.device)
+        dev = self.alloc(tuple(host.shape), host.dtype)
+        dev.copy_(host)
+        return dev
 
 
 class Part:
@@ -50,6 +61,17 @@ class Part:
 
     def workspace(self) -> dict[str, tuple[int, str]]:
         """Per-token workspace this part asks for: name -> (columns, 'act' | 'f32')."""
+        return {}
+
+    def fused_tensors(self) -> dict[str, tuple]:
+        """Tensors this part wants stored as consecutive rows of one matrix, in this order:
+        {name of the whole: (local names...)}.  The loader then fills the one matrix and `bind`
+        gets the whole under its name next to the pieces (views of its rows)."""
+        return {}
+
+    def device_tensors(self) -> dict[str, tuple]:
+        """Device tensors this part makes itself at bind, beyond its weights: name -> (shape, dtype).
+        The engine counts them in its memory plan; the part gets them through `rt.derived`."""
         return {}
 
     def bind(self, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:

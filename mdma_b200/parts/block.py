@@ -34,4 +34,4 @@ class PreNormBlock:
         a norm that does not do that gets x completed first."""
         if ctx.rt.gemm == "tensor" and not getattr(norm, "fuses_pending", False):
             from .. import ops_tensor
-            ops_tensor.flush_pending(x.device)
+            ops_tensor.flush_pending(x.device, ctx.rt.tc)

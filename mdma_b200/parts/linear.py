@@ -24,11 +24,11 @@ class Linear:
     def _run(self, mode: int, a: torch.Tensor, out: torch.Tensor, m: int, defer: bool = False) -> None:
         if self._tensor_ok:
             from .. import ops_tensor
-            ops_tensor.gemm(a, self.w, out, mode, self.w2, m, defer=defer)
+            ops_tensor.gemm(a, self.w, out, mode, self.w2, m, defer=defer, st=self.rt.tc)
         else:
             if self.rt.gemm == "tensor":
                 from .. import ops_tensor
-                ops_tensor.flush_pending(a.device)
+                ops_tensor.flush_pending(a.device, self.rt.tc)
             ops.gemm_simt(a, self.w, out, mode, self.w2, m)
 
     def store(self, a, out, m, defer: bool = False):

@@ -29,12 +29,12 @@ class RMSNorm(Part):
         n = n_rows if n_rows is not None else (None if rows is not None else ctx.n_tokens)
         if self.rt.gemm == "tensor":
             from .. import ops_tensor
-            pend = ops_tensor.take_pending(x, ops.GEMM_ACCUMULATE, ctx.n_tokens) if rows is None else None
+            pend = ops_tensor.take_pending(x, ops.GEMM_ACCUMULATE, ctx.n_tokens, self.rt.tc) if rows is None else None
             if pend is not None:
                 scratch, splits, stride = pend
                 ops.rmsnorm(x, self.weight, self.eps, out, None, n, scratch, splits, stride)
                 return
-            ops_tensor.flush_pending(x.device)
+            ops_tensor.flush_pending(x.device, self.rt.tc)
         ops.rmsnorm(x, self.weight, self.eps, out, rows, n)
 
     def resident_tensors(self):

@@ -57,23 +57,28 @@ class Rotary(Part):
         self.table_host = inverse_frequencies(self.rotary_dim, p["theta"], p.get("scaling"))
 
     def bind(self, tensors, rt):
+        if getattr(self, "rt", None) is rt and getattr(self, "inv_freq", None) is not None:
+            return                  # bound by its mixer and again by the model: one table
         super().bind(tensors, rt)
-        self.inv_freq = self.table_host.to(rt.device)
+        self.inv_freq = rt.derived(self.table_host)
 
     fuses_pending = True        # adds up a deferred K-split projection itself
 
     def resident_tensors(self):
         return []                 # the frequency table is derived, not a weight
 
+    def device_tensors(self):
+        return {"inv_freq": ((self.rotary_dim // 2,), torch.float32)}
+
     def encode_and_store(self, ctx, qkv, n_heads, n_kv_heads, head_dim, view, write_kv):
         partial, splits, stride = None, 0, 0
         if self.rt.gemm == "tensor":
             from .. import ops_tensor
-            pend = ops_tensor.take_pending(qkv, ops.GEMM_STORE, ctx.n_tokens)
+            pend = ops_tensor.take_pending(qkv, ops.GEMM_STORE, ctx.n_tokens, self.rt.tc)
             if pend is not None:
                 partial, splits, stride = pend
             else:
-                ops_tensor.flush_pending(qkv.device)
+                ops_tensor.flush_pending(qkv.device, self.rt.tc)
         ops.rope_cache_write(qkv, ctx.n_tokens, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot, self.inv_freq,
                              view.k if write_kv else None, view.v if write_kv else None,
                              view.page_table if write_kv else None, view.max_pages, view.page_size,

@@ -102,8 +102,11 @@ def resident_dtype(spec: TensorSpec, stored: torch.dtype, compute: torch.dtype) 
 
 
 def load_tensors(model_dir: str, expected: dict[str, TensorSpec], compute: torch.dtype,
-                 device: Optional[torch.device] = None) -> dict[str, torch.Tensor]:
-    """Validate the folder against `expected`, then fetch each tensor by name."""
+                 device: Optional[torch.device] = None, into: Optional[dict] = None) -> dict[str, torch.Tensor]:
+    """Validate the folder against `expected`, then fetch each tensor by name.  With `into`
+    (name -> a tensor of the right shape and resident dtype, e.g. a view of an engine's arena)
+    the values are copied there and no memory is taken for them here: the dtype is converted on
+    the host and the bytes go from the mapped file to their place."""
     files = open_model_files(model_dir)
     entries = {}
     for sf in files:
@@ -115,9 +118,20 @@ def load_tensors(model_dir: str, expected: dict[str, TensorSpec], compute: torch
         e = entries[name]
         t = by_file[e.file].tensor(name)
         dtype = resident_dtype(spec, e.dtype, compute)
-        if device is not None:
-            t = t.to(device=device, dtype=dtype, non_blocking=False)
+        if into is not None:
+            dst = into[name]
+            if dst.dtype != dtype or tuple(dst.shape) != tuple(spec.shape):
+                raise ValueError(f"{name}: the place prepared for it is {list(dst.shape)} {dst.dtype}, "
+                                 f"it is {list(spec.shape)} {dtype}")
+            dst.copy_(t.to(dtype=dtype))
+            out[name] = dst
+        elif device is not None:
+            out[name] = t.to(device=device, dtype=dtype, non_blocking=False).contiguous()
         else:
-            t = t.to(dtype=dtype)
-        out[name] = t.contiguous()
+            out[name] = t.to(dtype=dtype).contiguous()
     return out
+
+
+def stored_dtypes(model_dir: str) -> dict:
+    """name -> dtype as stored, from the headers alone."""
+    return {n: e.dtype for sf in open_model_files(model_dir) for n, e in sf.entries.items()}

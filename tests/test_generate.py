@@ -65,7 +65,6 @@ def test_sampled_generation_is_seeded_and_independent_of_batch_mates():
     from mdma_b200.engine import Engine
     from mdma_b200.engine.generate import Generator
     from mdma_b200.sampling import SamplingParams, uniform
-    from mdma_b200.sampling.sampler import DeviceSampler
     # and the tokens follow the plain sampler on the plain model's logits
     params = SamplingParams(0.8, 0.95, 0.05, 1.1, 64, 11)
     W = {k: v.float() for k, v in tensors.items()}
@@ -117,7 +116,7 @@ def test_command_line(tmp_path):
     res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mdma"), "plan", d, "--ctx", "64", "--json"],
                          capture_output=True, text=True, env=env)
     plan = json.loads(res.stdout)
-    assert plan["total_bytes"] == plan["weights_bytes"] + plan["cache_bytes"] + plan["workspace_bytes"]
+    assert plan["total_bytes"] == sum(v for k, v in plan.items() if k.endswith("_bytes") and k != "total_bytes")
 
 
 def test_engine_refuses_bad_steps_and_keeps_its_cache():
@@ -158,18 +157,76 @@ def test_missing_library_fails_loudly(monkeypatch):
 
 def test_plan_equals_what_is_held():
     """The memory plan, made from sizes alone, is what the engine then holds (the reference's rule:
-    src/model/arch/llama/tests.rs:8-66, src/model/planning/tests.rs:6-30)."""
+    src/model/arch/llama/tests.rs:8-66, src/model/planning/tests.rs:6-30): every category, the total, and
+    what the allocator says the process took; and generation takes nothing more, however long it runs."""
+    import gc
     from mdma_b200.engine import Engine
     from mdma_b200.engine.step import plan_only
     for cfg, seed, wdtype, dtype in ((TINY_A, 0, torch.float32, "float32"), (TINY_B, 1, torch.bfloat16, "bfloat16"),
                                      (TINY_C, 2, torch.float32, "bfloat16")):
         d, _, _ = make_model(cfg, seed, wdtype)
+        gc.collect()                    # engines of earlier tests give their memory back now, not in between
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated()
         eng = Engine(d, dtype=dtype, max_batch=3, max_context=128)
         held = eng.held_bytes()
-        for key in ("weights_bytes", "cache_bytes", "workspace_bytes"):
-            assert eng.plan[key] == held[key], (key, eng.plan[key], held[key])
-        alone = plan_only(d, dtype=dtype, max_batch=3, max_context=128)
-        assert alone["weights_bytes"] == held["weights_bytes"] and alone["cache_bytes"] == held["cache_bytes"]
+        assert eng.plan["total_bytes"] == held["total_bytes"] == sum(v for k, v in held.items() if k != "total_bytes")
+        for key, value in held.items():
+            assert eng.plan[key] == value, (key, eng.plan[key], value)
+        taken = torch.cuda.memory_allocated() - before
+        # one allocation; the allocator hands out segments of 2 MiB and counts a tail it cannot split off
+        assert 0 <= taken - eng.plan["total_bytes"] < (2 << 20), (taken, eng.plan["total_bytes"])
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        alone = plan_only(d, dtype=dtype, max_batch=3, max_context=128, sms=sms)
+        assert alone == eng.plan
+        prompts = prompts_for(cfg, (5, 40, 17), seed)
+        eng.generate(prompts, max_tokens=20)                    # warm: kernels loaded, graphs captured
+        eng.generate(prompts, max_tokens=20, temperature=0.7, seed=3)
+        torch.cuda.synchronize()
+        warm = torch.cuda.memory_allocated()
+        for seed2 in range(4):                                  # other options and seeds: the same graphs
+            eng.generate(prompts, max_tokens=30, temperature=0.9, top_p=0.9, seed=seed2)
+            eng.generate(prompts[::-1], max_tokens=30)
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == warm
+        assert len(eng.decode_session().graphs) <= 2 * 3        # (batch size 1..3) x (argmax, draw)
+        del eng
+
+
+def test_nothing_is_allocated_before_a_refusal(tmp_path):
+    """A folder with a wrong tensor, a configuration no kernel takes and a plan beyond the budget are all
+    refused before any device memory is taken (the reference counts its backend's allocations the same way:
+    src/model/arch/llama/preflight/tests.rs:98-116)."""
+    import json as _json
+    from mdma_b200 import WeightsError
+    from mdma_b200.engine import Engine, MemoryBudgetError
+    from mdma_b200.weights import write_safetensors
+    from mdma_b200.weights.safetensors_io import SafetensorsFile
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
+
+    def allocations():
+        return torch.cuda.memory_stats()["allocation.all.allocated"]
+    d, _, tensors = make_model(TINY_A, 0, torch.float32)
+    # a folder whose head has one row too few, and a stray tensor
+    bad = dict(tensors)
+    bad["lm_head.weight"] = bad["lm_head.weight"][:-1].contiguous()
+    bad["stray.bias"] = torch.zeros(3)
+    write_safetensors(str(tmp_path / "model.safetensors"), bad)
+    (tmp_path / "config.json").write_text(open(os.path.join(d, "config.json")).read())
+    n0 = allocations()
+    with pytest.raises(WeightsError):
+        Engine(str(tmp_path), dtype="float32", max_batch=2)
+    assert allocations() == n0
+    # a head wider than any attention kernel takes
+    wide = dict(TINY_A, head_dim=512)
+    with pytest.raises(ValueError, match="head_dim 512"):
+        Engine(config=wide, seed=0, dtype="float32", max_batch=2)
+    assert allocations() == n0
+    with pytest.raises(MemoryBudgetError):
+        Engine(d, dtype="float32", max_batch=2, vram_bytes=1 << 20, reserve_mib=0)
+    assert allocations() == n0
 
 
 def test_graph_replay_equals_eager():

@@ -191,13 +191,18 @@ def test_rope_cache_write_many_tokens(hd, rot, H, K):
     assert bool((kc.cpu()[mask] == 0).all()) and bool((vc.cpu()[mask] == 0).all())
 
 
-def fill_cache(seq_lens, K, hd, page, dtype, seed=0, scatter=True):
-    """Random keys/values for sequences, stored in shuffled pages. Returns dense and paged forms."""
+def fill_cache(seq_lens, K, hd, page, dtype, seed=0, scatter=True, poison=False):
+    """Random keys/values for sequences, stored in shuffled pages. Returns dense and paged forms.
+    `poison`: every cache row that belongs to no sequence (free pages, rows beyond a sequence's
+    length) holds NaN, as after an earlier occupant whose values were not finite."""
     g = torch.Generator().manual_seed(seed)
     n_pages_each = [-(-n // page) for n in seq_lens]
     total = sum(n_pages_each) + 3
     order = torch.randperm(total, generator=g).tolist() if scatter else list(range(total))
     kc, vc = paged_cache(total, page, K, hd, dtype)
+    if poison:
+        kc.fill_(float("nan"))
+        vc.fill_(float("nan"))
     max_pages = max(n_pages_each) + 1
     table = torch.zeros(len(seq_lens), max_pages, dtype=torch.int32)
     dense = []
@@ -216,16 +221,21 @@ def fill_cache(seq_lens, K, hd, page, dtype, seed=0, scatter=True):
 
 
 def reference_attention(q, dense, tok_seq, tok_pos, scale, window):
-    """q [T,H,D] float64; for each token attend over its sequence's keys [first, pos]."""
+    """q [T,H,D] float64.  Token t at position p of its sequence sees the keys [first, p], first = 0 or
+    p + 1 - window; kv head = head // group; s = (q.k) * scale; p = exp(s - max) / sum; o = sum p v
+    (src/backend/cpu.rs:530-590), in float64."""
     T, H, D = q.shape
     out = torch.zeros(T, H * D, dtype=torch.float64)
     for t in range(T):
         k, v = dense[tok_seq[t]]
         n = tok_pos[t] + 1
-        # plain_attention on a one-query problem: put the query last
-        qq = torch.zeros(n, H, D, dtype=torch.float64)
-        qq[-1] = q[t]
-        out[t] = plain_attention(qq, k[:n].double(), v[:n].double(), scale, window)[-1]
+        first = 0 if window == 0 else max(0, n - window)
+        kk, vv = k[first:n].double(), v[first:n].double()
+        group = H // kk.shape[1]
+        for h in range(H):
+            s = (kk[:, h // group, :] @ q[t, h]) * scale
+            p = torch.exp(s - s.max())
+            out[t, h * D:(h + 1) * D] = (p / p.sum()) @ vv[:, h // group, :]
     return out
 
 
@@ -290,23 +300,35 @@ class StepMeta:
 
 @pytest.mark.parametrize("H,K,hd,window", [(8, 2, 128, 0), (6, 2, 48, 0), (4, 4, 16, 0), (12, 2, 64, 0),
                                            (6, 1, 80, 0), (8, 2, 128, 100), (5, 5, 112, 33), (32, 8, 128, 0)])
-@pytest.mark.parametrize("case", ["prefill", "chunked", "decode", "decode_split", "prefill_tc", "chunked_tc"])
-def test_attention_tensor(H, K, hd, window, case):
+@pytest.mark.parametrize("case", ["prefill", "chunked", "decode", "decode_split", "decode_long", "decode_many",
+                                  "decode_page16", "prefill_tc", "chunked_tc"])
+@pytest.mark.parametrize("poison", [False, True])
+def test_attention_tensor(H, K, hd, window, case, poison):
     """The tensor-core attention against the float64 statement of the reference's loop:
-    whole prompts, prompts on top of a cached prefix, single tokens, and keys split over blocks."""
+    whole prompts, prompts on top of a cached prefix, single tokens (one block of eight warps; keys
+    split over blocks, by hand and by the kernel's own choice for a long context; so many sequences
+    that blocks of four warps are taken; pages that the tile loads cannot use), with and without NaN in
+    every cache row that belongs to nobody."""
     from mdma_b200 import ops_tensor
     torch.manual_seed(H * 1000 + hd)
-    page = 64
+    page = 16 if case == "decode_page16" else 64
     impl = "tc" if case.endswith("_tc") else "mma"
     case = case.replace("_tc", "")
     if case == "prefill":
         cached, new = [0, 0, 0], [150, 3, 65]
     elif case == "chunked":
         cached, new = [70, 129, 1], [100, 20, 64]
+    elif case == "decode_long":
+        cached, new = [2500, 1030, 7], [1, 1, 1]          # beyond 1024: the kernel splits the keys itself
+    elif case == "decode_many":
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        n = -(-2 * sms // K) + 1                          # sequences x kv heads >= 2 x SMs: four-warp blocks, no split
+        g = torch.Generator().manual_seed(7)
+        cached, new = torch.randint(0, 200, (n,), generator=g).tolist(), [1] * n
     else:
         cached, new = [299, 0, 64, 1000], [1, 1, 1, 1]
     lens = [c + n for c, n in zip(cached, new)]
-    kc, vc, table, max_pages, dense = fill_cache(lens, K, hd, page, torch.bfloat16, seed=hd)
+    kc, vc, table, max_pages, dense = fill_cache(lens, K, hd, page, torch.bfloat16, seed=hd, poison=poison)
     meta = StepMeta(cached, new)
     T = meta.n_tokens
     q = (torch.randn(T, (H + 2 * K) * hd, device=DEV)).bfloat16()
@@ -326,28 +348,36 @@ def test_attention_tensor(H, K, hd, window, case):
     assert bool((out[T:] == 9.0).all())
 
 
-def test_attention_tensor_finds_one_far_key_and_the_window_edge():
+@pytest.mark.parametrize("path", ["decode", "decode_split", "prefill_tc", "chunked_tc", "chunked_mma"])
+def test_attention_tensor_finds_one_far_key_and_the_window_edge(path):
+    """One key among 900 is made to dominate the last query's head 0: inside the window it must be
+    found, one place before the window it must not be seen; on every kernel that serves the engine."""
     from mdma_b200 import ops_tensor
     H, K, hd, page = 4, 1, 64, 64
     kc, vc, table, max_pages, dense = fill_cache([900], K, hd, page, torch.bfloat16, seed=5)
     k, v = dense[0]
-    q = torch.randn(1, H * hd).bfloat16()
+    cached, new = {"decode": (899, 1), "decode_split": (899, 1), "prefill_tc": (0, 900),
+                   "chunked_tc": (600, 300), "chunked_mma": (880, 20)}[path]
+    q = torch.randn(new, (H + 2 * K) * hd).bfloat16()
     for target, window, seen in ((123, 0, True), (899 - 99, 100, True), (899 - 100, 100, False)):
         kk = k.clone()
-        kk[target, 0] = (q[0, :hd].float() * 3.0).bfloat16()          # head 0 points at one key
+        kk[target, 0] = (q[-1, :hd].float() * 3.0).bfloat16()         # head 0 of the last token points at one key
         pg = int(table[0, target // page])
         kc2 = kc.clone()
         kc2[pg, target % page, 0] = kk[target, 0].to(DEV)
-        meta = StepMeta([899], [1])
-        out = torch.zeros(1, H * hd, device=DEV, dtype=torch.bfloat16)
+        meta = StepMeta([cached], [new])
+        out = torch.zeros(new, H * hd, device=DEV, dtype=torch.bfloat16)
 
         class View:
             pass
         view = View()
         view.k, view.v, view.page_table, view.max_pages, view.page_size = kc2, vc, table, max_pages, page
-        ops_tensor.attention(meta, q.to(DEV), view, out, H, K, hd, window, 1.0, splits=3)
-        hit = (out[0, :hd].float().cpu() - v[target, 0].float()).abs().max().item() < 0.05
-        assert hit == seen, (target, window)
+        ops_tensor.attention(meta, q.to(DEV), view, out, H, K, hd, window, 1.0,
+                             splits=3 if path == "decode_split" else None,
+                             impl="tc" if path.endswith("_tc") else "mma")
+        ops_tensor.check_status(torch.device(DEV))
+        hit = (out[-1, :hd].float().cpu() - v[target, 0].float()).abs().max().item() < 0.05
+        assert hit == seen, (path, target, window)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 5, 3), (67, 130, 100), (5, 331, 120), (200, 64, 17)])

@@ -135,7 +135,7 @@ def test_toy_architecture_builds_and_steps(tmp_path, dtype, tol):
     sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
     W = {n: sf.tensor(n).clone() for n in sf.entries}
     assert "l2.attn.k_proj.weight" not in W and "l1.mix.in.weight" in W     # the sharing layer owns no k/v
-    eng = Engine(d, dtype=dtype, max_batch=3, max_context=128)
+    eng = Engine(d, dtype=dtype, max_batch=3, max_context=128, logit_rows=128)
     assert len(eng.cache.groups) == 1 and eng.cache.groups[0].sites == [0]  # one cache site, read twice
     assert sorted(eng.cache.states) == [1, 3]                               # two runs, two states
     g = torch.Generator().manual_seed(0)
@@ -303,7 +303,7 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path):
     W["l0.moe.router.weight"] = W["l0.moe.router.weight"] * 40      # decisive routing, all experts used
     W["pos.table"] = W["pos.table"] * 10
     write_safetensors(os.path.join(d, "model.safetensors"), W)
-    eng = Engine(d, dtype="float32", max_batch=2, max_context=64)
+    eng = Engine(d, dtype="float32", max_batch=2, max_context=64, logit_rows=64)
     g = torch.Generator().manual_seed(1)
     seqs = [torch.randint(0, V, (n,), generator=g).tolist() for n in (40, 13)]
     ref = [plain_toy_routed(cfg, W, s).numpy() for s in seqs]
