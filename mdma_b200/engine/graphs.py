@@ -19,6 +19,7 @@ whether tokens are drawn or the largest logit is taken.
 """
 from __future__ import annotations
 
+import gc
 from typing import Optional, Sequence
 
 import numpy as np
@@ -168,8 +169,18 @@ class DecodeSession:
                     self._body(B, draws)
                     self.launches_per_step = ops.LAUNCHES - before
                     g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g):
-                        self._body(B, draws)
+                    # The collector must not run while the stream is captured: finalising an engine
+                    # that went out of use (its graphs, events, pinned buffers) makes CUDA calls that
+                    # are not allowed then and would spoil the capture.
+                    gc.collect()
+                    was_enabled = gc.isenabled()
+                    gc.disable()
+                    try:
+                        with torch.cuda.graph(g):
+                            self._body(B, draws)
+                    finally:
+                        if was_enabled:
+                            gc.enable()
                     self.graphs[key] = g
                 else:
                     g.replay()

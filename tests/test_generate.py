@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from plain_llama import plain_forward, plain_generate, plain_sample
-from tiny import TINY_A, TINY_B, TINY_C, make_model
+from tiny import SHARP, TINY_A, TINY_B, TINY_C, TINY_D, make_model
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -251,3 +251,68 @@ def test_engine_generate_method():
     outs = eng.generate(p, max_tokens=5)
     assert [o.tokens for o in outs] == [plain_generate(c, tensors, q, 5) for q in p]
     assert eng.generate(p, max_tokens=5)[0].tokens == outs[0].tokens       # slots were given back: it runs again
+
+
+def test_generation_across_the_1024_bucket_and_run_ahead():
+    """Prompts of 1,015 and 40 tokens, 30 tokens each: the longer sequence passes 1,024 positions, where
+    the decode graphs of the next bucket are captured and the attention kernel changes its variant.
+    Replayed in runs of eight steps, in runs of one, and step by step without graphs: the same tokens."""
+    from mdma_b200.engine import Engine
+    from mdma_b200.engine.generate import Generator
+    from mdma_b200.sampling import SamplingParams
+    d, c, tensors = make_model(TINY_D, 3, torch.bfloat16, std_scale=SHARP)
+    prompts = prompts_for(TINY_D, (1015, 40, 300), 6)
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(d, dtype=dtype, max_batch=3, max_context=1100)
+        for params in (SamplingParams.greedy(), SamplingParams(0.8, 0.95, 0.05, 1.2, 64, 9)):
+            runs = Generator(eng, run_ahead=8).generate(prompts, 30, params)
+            ones = Generator(eng, run_ahead=1).generate(prompts, 30, params)
+            eager = Generator(eng, use_graphs=False).generate(prompts, 30, params)
+            assert [o.tokens for o in runs] == [o.tokens for o in eager], (dtype, params)
+            assert [o.tokens for o in ones] == [o.tokens for o in eager], (dtype, params)
+            assert all(len(o.tokens) == 30 for o in runs)
+        # a stop token inside a run: the sequence ends there, the others go on
+        free = Generator(eng).generate(prompts, 30)
+        stop = [free[1].tokens[11]]
+        cut = Generator(eng, run_ahead=8).generate(prompts, 30, stop_ids=stop)
+        step = Generator(eng, use_graphs=False).generate(prompts, 30, stop_ids=stop)
+        assert [o.tokens for o in cut] == [o.tokens for o in step]
+        assert cut[1].finish_reason == "stop" and len(cut[1].tokens) <= 11
+        eng.cache.check()
+        assert not eng.cache.lengths                           # every slot was given back
+        del eng
+
+
+def test_logits_of_the_replayed_decode_step_match_the_oracle():
+    """The graph-replayed decode step lays out its own inputs; its logits (not only its tokens) are
+    compared with the plain implementation, across 1,024 positions, in both dtypes."""
+    from mdma_b200.engine import Engine, StepEntry
+    from mdma_b200.sampling import SamplingParams
+    from replay_util import assert_close
+    d, c, tensors = make_model(TINY_D, 3, torch.bfloat16, std_scale=SHARP)
+    W = {k: v.float() for k, v in tensors.items()}
+    prompts = prompts_for(TINY_D, (1019, 37), 8)
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(d, dtype=dtype, max_batch=2, max_context=1100)
+        slots = [eng.acquire() for _ in prompts]
+        logits = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        tokens, _ = eng.sampler.sample(logits, SamplingParams.greedy(), [0, 1], [0, 0])
+        seqs = [list(p) + [t] for p, t in zip(prompts, tokens)]
+        sess = eng.decode_session()
+        sess.start(slots, tokens)
+        kept = []
+        for _ in range(12):
+            sess.run(1)
+            toks, flags = sess.read()[-1]
+            assert flags == [0, 0]
+            kept.append(sess.logits[:2].double().cpu().numpy())
+            for q, t in zip(seqs, toks):
+                q.append(t)
+        assert len(sess.graphs) == 2                            # one per bucket of 1,024 positions
+        for i, q in enumerate(seqs):
+            ref = plain_forward(c, W, q[:-1], torch.float64).numpy()
+            for j in range(12):
+                assert_close(kept[j][i], ref[len(prompts[i]) + j], dtype, f"replayed step {j}, sequence {i}")
+        for s in slots:
+            eng.release(s)
+        del eng

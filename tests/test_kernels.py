@@ -585,6 +585,54 @@ def test_sample_matches_the_host_sampler(vocab, opts, impl):
     assert flags.sum().item() == 0
 
 
+@pytest.mark.parametrize("opts", [dict(temperature=0.8, top_p=0.95, min_p=0.05, repetition_penalty=1.1),
+                                  dict(temperature=0.8, top_p=1.0, min_p=0.0, repetition_penalty=1.0)])
+def test_sample_at_the_vocabulary_of_the_benchmark(opts):
+    """128,256 entries, where a block of the cluster holds 64 KB of the row: the kernel's own choice of
+    variant, four rows, the default options and temperature alone; also with the options read from
+    device memory, as the replayed decode loop passes them."""
+    ops = ops_mod()
+    from mdma_b200.sampling import SamplingParams
+    from mdma_b200.sampling.sampler import params_words
+    vocab, n = 128256, 4
+    torch.manual_seed(11)
+    logits = torch.randn(n, vocab) * 2.5
+    logits[1, 100] = logits[1, 128255] = logits[1].max() + 0.5    # tied leaders, one of them the last entry
+    hist = torch.randint(0, vocab, (n, 64), dtype=torch.int32)
+    hist[:, 0] = logits.argmax(1).int()
+    hlen = torch.full((n,), 64, dtype=torch.int32)
+    u = torch.tensor([0.03, 0.5, 0.77, 0.999])
+    tok = torch.zeros(n, dtype=torch.int32, device=DEV)
+    flags = torch.zeros(n, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(ops.sample_scratch_words(n, vocab), device=DEV)
+    args = (opts["temperature"], opts["top_p"], opts["min_p"], opts["repetition_penalty"], 64)
+    ops.sample(logits.to(DEV), u.to(DEV), tok, scratch, *args, hist.to(DEV), hlen.to(DEV), flags)
+    got = tok.tolist()
+    assert flags.sum().item() == 0
+    if opts["min_p"] > 0:             # a handful of candidates: the plain sampler's token exactly
+        want = [plain_sample(logits[i].tolist(), hist[i].tolist(), float(u[i]), *args) for i in range(n)]
+        assert got == want
+    else:
+        # Every entry is a candidate, each with about 1e-5 of the mass: a float32 running sum over 128,256
+        # terms (the plain sampler's) is itself uncertain by more than that, so the check is made in
+        # float64: the uniform number must lie in the selected token's interval of the descending order
+        # (ties by token id), give or take 1e-6 of the mass for the float32 exponentials.
+        for i in range(n):
+            x = logits[i].double() / opts["temperature"]      # penalty 1: the history does not matter
+            p = torch.exp(x - x.max())
+            p = p / p.sum()
+            order = sorted(range(vocab), key=lambda t: (-float(p[t]), t))
+            cum = torch.cumsum(p[order], 0)
+            r = order.index(got[i])
+            lo = float(cum[r - 1]) if r else 0.0
+            assert lo - 1e-6 <= float(u[i]) <= float(cum[r]) + 1e-6, (i, got[i], lo, float(u[i]), float(cum[r]))
+    words = torch.from_numpy(params_words(SamplingParams(*args, seed=0))).to(DEV)
+    tok2 = torch.zeros_like(tok)
+    ops.sample(logits.to(DEV), u.to(DEV), tok2, scratch, 1.0, 1.0, 0.0, 1.0, 0, hist.to(DEV), hlen.to(DEV), flags,
+               dev_params=words)
+    assert tok2.tolist() == got
+
+
 @pytest.mark.parametrize("impl", [1, 2])
 def test_sample_follows_the_distribution(impl):
     ops = ops_mod()

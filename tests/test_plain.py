@@ -97,3 +97,66 @@ def test_float32_and_float64_agree():
     a = plain_forward(c, tensors, ids, torch.float32).double()
     b = plain_forward(c, tensors, ids, torch.float64)
     assert (a - b).abs().max() < 2e-5
+
+
+def test_the_two_plain_implementations_agree():
+    """tests/plain_llama.py (PyTorch) and tests/plain_ref.cpp (C++ scalar loops, rotation as a complex
+    product, llama3 scaling stated on frequencies) were written separately from the formulas; they must
+    give the same logits at every place, for every shape and option of the tiny configurations."""
+    from plain_llama import plain_inv_freq
+    from plain_ref import ref_forward, ref_inv_freq
+    from tiny import SHARP, TINY_C, TINY_D
+    for cfg, seed in ((TINY_A, 0), (TINY_B, 1), (TINY_C, 2), (TINY_D, 3), (dict(TINY_A, rope_layout="split_half"), 4),
+                      (dict(TINY_B, rope_layout="interleaved", tie_word_embeddings=False), 5)):
+        _, c, tensors = make_model(cfg, seed, torch.float32, std_scale=SHARP)
+        g = torch.Generator().manual_seed(seed)
+        ids = torch.randint(0, cfg["vocab_size"], (61,), generator=g).tolist()
+        a = plain_forward(c, tensors, ids, torch.float64)
+        b = ref_forward(c, tensors, ids)
+        assert (a - b).abs().max() < 1e-12, cfg
+        D = c.get("head_dim") or c["hidden_size"] // c["num_attention_heads"]
+        fa = plain_inv_freq(D, c.get("rope_theta", 10000.0), c.get("rope_scaling"))
+        fb = ref_inv_freq(D, c.get("rope_theta", 10000.0), c.get("rope_scaling"))
+        assert torch.equal(fa.double(), fb)
+
+
+def test_llama3_table_by_hand():
+    """The scaled table at values worked out by hand: theta 16, head 8, L = 64, factor 8, low 1, high 4.
+    f = 1, 1/2, 1/4, 1/8; wavelengths 6.28, 12.6, 25.1, 50.3.  L/high = 16, L/low = 64: the first two
+    stay, the last two lie in the band: smooth = (64/25.13 - 1)/3 = 0.5155 and (64/50.27 - 1)/3 = 0.0911."""
+    from plain_llama import plain_inv_freq
+    f = plain_inv_freq(8, 16.0, dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                     original_max_position_embeddings=64)).double()
+    two_pi = 2 * math.pi
+    s2, s3 = (64 / (two_pi * 4) - 1) / 3, (64 / (two_pi * 8) - 1) / 3
+    want = [1.0, 0.5, (1 - s2) * 0.25 / 8 + s2 * 0.25, (1 - s3) * 0.125 / 8 + s3 * 0.125]
+    assert torch.allclose(f, torch.tensor(want, dtype=torch.float64), rtol=1e-6)
+    # beyond the band everything is divided by the factor
+    f = plain_inv_freq(8, 16.0, dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                     original_max_position_embeddings=4)).double()
+    assert torch.allclose(f, torch.tensor([1.0, 0.5, 0.25, 0.125], dtype=torch.float64) / 8, rtol=1e-6)
+
+
+def test_the_oracle_tells_a_wrong_cache_row_from_rounding():
+    """With the tests' weights, changing ONE token anywhere among the first 96 of 97 moves some later
+    row of logits by far more than the bfloat16 tolerances of tests/replay_util.py (0.05 absolute, 2 % of
+    a row's deviation): at least 5 times for the least influential token of any shape, and 10 times for
+    the median token.  So a stale, missing or misplaced cache row cannot hide under the tolerance."""
+    from replay_util import TOL_BF16_ABS, TOL_BF16_ROW
+    from tiny import SHARP, TINY_C, TINY_D
+    for cfg, seed, wd in ((TINY_A, 0, torch.float32), (TINY_B, 1, torch.bfloat16), (TINY_C, 2, torch.bfloat16),
+                          (TINY_D, 3, torch.bfloat16)):
+        _, c, tensors = make_model(cfg, seed, wd, std_scale=SHARP)
+        W = {k: v.float() for k, v in tensors.items()}
+        g = torch.Generator().manual_seed(seed)
+        ids = torch.randint(0, cfg["vocab_size"], (97,), generator=g).tolist()
+        base = plain_forward(c, W, ids, torch.float64)
+        moved_abs, moved_row = [], []
+        for j in range(0, 96, 5):
+            other = list(ids)
+            other[j] = (other[j] + 1) % cfg["vocab_size"]
+            delta = plain_forward(c, W, other, torch.float64)[j + 1:] - base[j + 1:]
+            moved_abs.append(delta.abs().max().item())
+            moved_row.append((delta.pow(2).mean(1).sqrt() / base[j + 1:].std(1)).max().item())
+        assert min(moved_abs) >= 5 * TOL_BF16_ABS and min(moved_row) >= 5 * TOL_BF16_ROW, (cfg, min(moved_abs), min(moved_row))
+        assert sorted(moved_abs)[len(moved_abs) // 2] >= 10 * TOL_BF16_ABS

@@ -27,12 +27,33 @@ TINY_C = dict(
     tie_word_embeddings=False, max_position_embeddings=512)
 
 
+# Matrices N(0, 0.02 * SHARP): the tiny models' logits then have a standard deviation of 0.6-0.9 and
+# their attention is far from uniform, so that a wrong or missing cache row moves the logits by much
+# more than bfloat16 rounding does.  Measured on a B200 over these four shapes (97 tokens, all places):
+# at 0.02 the bfloat16 engine's largest error is 0.003-0.004 and the least influential single token
+# moves some later logit by 0.012-0.030 (3.6-11 times the error); at 0.08 the error is 0.023-0.033 and
+# that token's effect 0.31-0.47 (9-16 times); at 0.12 attention is so sharp that some tokens hardly
+# matter (4-10 times).  So the tests run at 0.08.
+SHARP = 4.0
+
+# a fourth shape: context beyond 2,048 (decoding crosses the 1,024-position bucket of the decode graphs
+# and the attention kernel's change of variant there) and 8 kv heads
+TINY_D = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama",
+    num_hidden_layers=2, hidden_size=128, num_attention_heads=16, num_key_value_heads=8, head_dim=16,
+    intermediate_size=144, vocab_size=200, rope_theta=100000.0,
+    rope_scaling=dict(rope_type="llama3", factor=4.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=512),
+    rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=2304)
+
+
 def make_model(cfg: dict, seed: int, dtype=torch.float32, root=None, std_scale: float = 1.0):
-    """Write a model folder into a fresh temporary directory; returns (dir, config dict, tensors)."""
+    """Write a model folder into a fresh temporary directory; returns (dir, config dict, tensors).
+    Matrices are N(0, 0.02 * std_scale)."""
     from mdma_b200.weights import write_random_model
     from mdma_b200.weights.safetensors_io import SafetensorsFile
     d = tempfile.mkdtemp(prefix="mdma_tiny_", dir=root)
-    write_random_model(d, cfg, seed, dtype)
+    write_random_model(d, cfg, seed, dtype, std=0.02 * std_scale)
     sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
     tensors = {n: sf.tensor(n).clone() for n in sf.entries}
     return d, json.load(open(os.path.join(d, "config.json"))), tensors
