@@ -37,4 +37,27 @@ int mdma_attention_mma_paged(const void* q, int q_stride, const void* k_cache, c
                                 head_dim, window, scale, splits, scratch, scratch_floats, stream, n_pages, status);
 }
 
+// One token per sequence with the rotary encoding and the cache write inside the attention kernel:
+// `qkv` holds the step's projection rows, not rotated; with `proj_splits` > 0 the rows are instead the sums
+// of that many float partial rows at `proj_partial` (`proj_split_stride` floats apart).  The kernel writes
+// the rotated key and the value of every token to the caches.
+int mdma_attention_decode_rotary(const void* qkv, int q_stride, const float* proj_partial, int proj_splits,
+                                 long proj_split_stride, const float* inv_freq, int rotary_dim, int interleaved,
+                                 void* k_cache, void* v_cache, int n_pages, const int* seq_start, const int* seq_pos0,
+                                 const int* seq_slot, const int* page_table, int max_pages, int page_size, void* out,
+                                 int n_seqs, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                                 int splits, float* scratch, long scratch_floats, int* status, cudaStream_t stream) {
+    FusedRotary fz;
+    fz.inv_freq = inv_freq; fz.rotary_dim = rotary_dim; fz.interleaved = interleaved;
+    fz.partial = proj_splits > 0 ? proj_partial : nullptr; fz.splits = proj_splits; fz.split_stride = proj_split_stride;
+    fz.width = (n_heads + 2 * n_kv_heads) * head_dim;
+    return launch_attention_mma(qkv, q_stride, k_cache, v_cache, seq_start, seq_pos0, seq_slot, page_table, max_pages,
+                                page_size, out, n_seqs, n_seqs, 1, n_heads, n_kv_heads, head_dim, window, scale, splits,
+                                scratch, scratch_floats, stream, n_pages, status, &fz);
+}
+
+int mdma_attention_fused_rotary_supported(int n_heads, int n_kv_heads, int head_dim, int page_size, int rotary_dim) {
+    return attention_fused_rotary_supported(n_heads, n_kv_heads, head_dim, page_size, rotary_dim);
+}
+
 }  // extern "C"

@@ -62,6 +62,14 @@ struct AttnParams {
     int n_heads, n_kv_heads, head_dim, group, tile_tokens, window, splits;
     float scale_log2;                               // scale * log2(e)
     int* status;                                    // optional device word, set non-zero if a wait ran out
+    // Decode with the rotary encoding done here (`rot_inv_freq` not null): the step's projection rows are
+    // `q` (bfloat16, not yet rotated) or, with `proj_splits` > 0, the sum of that many float partial rows
+    // [split][token][proj_width]; the block rotates its query heads and its key head, rounds them to
+    // bfloat16, writes the key and the value to the cache row of the token's position and uses them from
+    // shared memory, so that no tile it fetches depends on the kernel before it.
+    const float* rot_inv_freq; int rotary_dim; int rot_interleaved;
+    const float* proj_partial; int proj_splits; long proj_split_stride; int proj_width;
+    __nv_bfloat16* k_cache_w; __nv_bfloat16* v_cache_w;
 };
 
 // Tile shared-memory rows are DMAX elements wide; 16-byte chunk c of row r sits at chunk c ^ (r & 7).
@@ -470,10 +478,11 @@ attention_decode_kernel(const AttnParams p) {
 // tile load, completion on the warp's own mbarrier) instead of 16-byte cp.async copies, whose address
 // arithmetic was two thirds of the instructions.  Needs page_size to be a multiple of KB.  A tile is
 // stored as halves of 64 head elements: [KB keys x 128 bytes] with the 128-byte swizzle.
-// NW warps per block: four (three blocks per SM) when the keys are split over blocks, eight when one
-// block takes all keys of a short context, which needs no merge kernel.
+// NW warps per block.  All blocks should run at once (a second, short round of blocks costs as
+// much as the first): eight warps and one block per SM while the blocks are no more than the SMs, else
+// four, three or two warps with three, four or five blocks per SM.
 template <int DMAX, int KB, int NW>
-__global__ void __launch_bounds__(NW * 32, NW == 4 ? 3 : 1)
+__global__ void __launch_bounds__(NW * 32, NW == 8 ? 1 : NW == 4 ? 3 : NW == 3 ? 4 : 5)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const AttnParams p) {
     constexpr int kChunks = DMAX / 8;
@@ -487,6 +496,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const uint32_t bars = sQ + 16 * DMAX * 2;
     const uint32_t kbar = bars + warp * 16, vbar = kbar + 8;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + NW * 2 * kTile + 16 * DMAX * 2 + NW * 16);
+    // with the rotary encoding done here: this token's rotated key and its value (bfloat16), sines and cosines
+    constexpr int kFreshOff = NW * 2 * kTile + 16 * DMAX * 2 + NW * 16 + 64;
+    __nv_bfloat16* fresh_k = reinterpret_cast<__nv_bfloat16*>(smem + kFreshOff);
+    __nv_bfloat16* fresh_v = fresh_k + DMAX;
+    float* sincos = reinterpret_cast<float*>(smem + kFreshOff + 4 * DMAX);
+    const bool fused = p.rot_inv_freq != nullptr;
     auto kv_offset = [](int row, int chunk) -> uint32_t {      // 16-byte chunk of a key row inside a tile
         return (uint32_t)((chunk >> 3) * kHalf + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
     };
@@ -523,20 +538,82 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     };
     int blk = b0 + warp;
     if (*abort_flag != 0) blk = b1;
-    const bool early = blk < b1 && blk != blk_hi - 1;
+    // (with the rotary encoding done here the row of the own token is replaced in shared memory, so
+    // the last tile does not depend on the kernel before either)
+    const bool early = blk < b1 && (fused || blk != blk_hi - 1);
     if (early && lane == 0) { load_tile(&map_k, sK, kbar, blk); load_tile(&map_v, sV, vbar, blk); }
+    if (fused) {
+        // sines and cosines of this position (no dependence on the kernel before); the Q tile starts as zeros
+        const int half = p.rotary_dim / 2;
+        for (int i = threadIdx.x; i < half; i += NW * 32) {
+            float sn, cs;
+            sincosf((float)pos * p.rot_inv_freq[i], &sn, &cs);
+            sincos[i] = sn; sincos[half + i] = cs;
+        }
+        for (int i = threadIdx.x; i < 16 * kChunks; i += NW * 32)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sQ + i * 16), "r"(0u) : "memory");
+    }
     chain_wait();
     if (!early && blk < b1 && lane == 0) { load_tile(&map_k, sK, kbar, blk); load_tile(&map_v, sV, vbar, blk); }
-    // Q rows (heads of the group) -> shared, zero beyond G and beyond D
-    for (int i = threadIdx.x; i < 16 * kChunks; i += NW * 32) {
-        const int r = i / kChunks, c = i % kChunks;
-        const bool valid = r < G && c < d_chunks;
-        const __nv_bfloat16* src = p.q + (size_t)token * p.q_stride + (size_t)(kvh * G + (valid ? r : 0)) * D + (valid ? c : 0) * 8;
-        cp_async_16(sQ + tile_offset<DMAX>(r, c), src, valid);
+    if (fused) {
+        __syncthreads();                                 // sines, cosines and the zeroed tile are in place
+        const int half = p.rotary_dim / 2, tail = D - p.rotary_dim;
+        const __nv_bfloat16* row = p.q + (size_t)token * p.q_stride;
+        const float* prow = p.proj_partial + (size_t)token * p.proj_width;
+        auto load = [&](int col) -> float {              // the projection's value: as stored, or its partial sums in split order
+            if (p.proj_splits == 0) return __bfloat162float(row[col]);
+            float a = 0.f;
+            int sidx = 0;
+            for (; sidx + 4 <= p.proj_splits; sidx += 4) {       // four loads in flight, added in order
+                const float* src = prow + (size_t)sidx * p.proj_split_stride + col;
+                const float v0 = __ldcg(src), v1 = __ldcg(src + p.proj_split_stride),
+                            v2 = __ldcg(src + 2 * p.proj_split_stride), v3 = __ldcg(src + 3 * p.proj_split_stride);
+                a += v0; a += v1; a += v2; a += v3;
+            }
+            for (; sidx < p.proj_splits; ++sidx) a += __ldcg(prow + (size_t)sidx * p.proj_split_stride + col);
+            return a;
+        };
+        uint8_t* q_tile = smem + NW * 2 * kTile;
+        auto q_elem = [&](int r, int d) -> __nv_bfloat16* {
+            return reinterpret_cast<__nv_bfloat16*>(q_tile + tile_offset<DMAX>(r, d >> 3) + (d & 7) * 2);
+        };
+        const int q_col0 = kvh * G * D, k_col0 = (p.n_heads + kvh) * D, v_col0 = (p.n_heads + p.n_kv_heads + kvh) * D;
+        for (int i = threadIdx.x; i < (G + 1) * half; i += NW * 32) {        // the G query heads, then the key head
+            const int r = i / half, pr = i % half;
+            const int d0 = p.rot_interleaved ? 2 * pr : pr, d1 = p.rot_interleaved ? 2 * pr + 1 : pr + half;
+            const int col = r < G ? q_col0 + r * D : k_col0;
+            const float x0 = load(col + d0), x1 = load(col + d1);
+            const float sn = sincos[pr], cs = sincos[half + pr];
+            const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn), y1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
+            if (r < G) { *q_elem(r, d0) = y0; *q_elem(r, d1) = y1; }
+            else { fresh_k[d0] = y0; fresh_k[d1] = y1; }
+        }
+        for (int i = threadIdx.x; i < (G + 1) * tail; i += NW * 32) {        // beyond the rotated width: as it is
+            const int r = i / tail, d = p.rotary_dim + i % tail;
+            const __nv_bfloat16 y = __float2bfloat16_rn(load((r < G ? q_col0 + r * D : k_col0) + d));
+            if (r < G) *q_elem(r, d) = y; else fresh_k[d] = y;
+        }
+        for (int i = threadIdx.x; i < D; i += NW * 32) fresh_v[i] = __float2bfloat16_rn(load(v_col0 + i));
+        __syncthreads();
+        // the block that holds the last tile keeps the token's key and value for later steps
+        if (b1 == blk_hi && b0 < b1 && threadIdx.x < 2 * d_chunks) {
+            const int which = threadIdx.x / d_chunks, c = threadIdx.x % d_chunks;
+            const size_t cache_row = (((size_t)pages[pos / p.page_size] * p.page_size + pos % p.page_size) * p.n_kv_heads + kvh) * D;
+            __nv_bfloat16* dst = (which ? p.v_cache_w : p.k_cache_w) + cache_row + c * 8;
+            *reinterpret_cast<uint4*>(dst) = reinterpret_cast<const uint4*>(which ? fresh_v : fresh_k)[c];
+        }
+    } else {
+        // Q rows (heads of the group) -> shared, zero beyond G and beyond D
+        for (int i = threadIdx.x; i < 16 * kChunks; i += NW * 32) {
+            const int r = i / kChunks, c = i % kChunks;
+            const bool valid = r < G && c < d_chunks;
+            const __nv_bfloat16* src = p.q + (size_t)token * p.q_stride + (size_t)(kvh * G + (valid ? r : 0)) * D + (valid ? c : 0) * 8;
+            cp_async_16(sQ + tile_offset<DMAX>(r, c), src, valid);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();                                 // Q is visible to all warps
     }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();                                     // Q is visible to all warps
     uint32_t phase = 0;
 
     uint32_t qf[DMAX / 16][4];
@@ -552,6 +629,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
     for (; blk < b1; blk += NW) {
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(kbar, phase, abort_flag))) break;     // this tile's K has landed
+        const bool own_tile = fused && blk == blk_hi - 1;      // the tile of the token's own position
+        if (own_tile) {
+            if (lane < d_chunks)
+                *reinterpret_cast<uint4*>(smem + (sK - s0) + kv_offset(pos - blk * KB, lane)) = reinterpret_cast<const uint4*>(fresh_k)[lane];
+            __syncwarp();
+        }
         float s[KB / 8][4];
 #pragma unroll
         for (int n = 0; n < KB / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
@@ -619,6 +702,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                     if (r < r_lo || r > r_hi)
                         asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sV + h * kHalf + r * 128 + c * 16), "r"(0u) : "memory");
                 }
+                __syncwarp();
+            }
+            if (own_tile) {
+                if (lane < d_chunks)
+                    *reinterpret_cast<uint4*>(smem + (sV - s0) + kv_offset(pos - blk * KB, lane)) = reinterpret_cast<const uint4*>(fresh_v)[lane];
                 __syncwarp();
             }
         }
@@ -750,13 +838,25 @@ static int make_cache_map(CUtensorMap* out, const void* cache, int n_pages, int 
     return 0;
 }
 
+// The rotary encoding and the cache write done inside the decode kernel (see AttnParams).
+struct FusedRotary {
+    const float* inv_freq; int rotary_dim; int interleaved;
+    const float* partial; int splits; long split_stride; int width;      // K-split partial sums of the projection, or none
+};
+// Whether a decode step with these sizes can take the fused form (it needs the tile loads by TMA).
+static inline int attention_fused_rotary_supported(int n_heads, int n_kv_heads, int head_dim, int page_size, int rotary_dim) {
+    if (!attention_mma_supported(n_heads, n_kv_heads, head_dim)) return 0;
+    return (n_heads / n_kv_heads <= 16 && page_size % 32 == 0 && rotary_dim % 2 == 0 && rotary_dim >= 2 &&
+            rotary_dim <= head_dim && head_dim % 8 == 0) ? 1 : 0;
+}
+
 // `n_pages` > 0 tells how many pages the caches hold and lets the decode kernel fetch tiles by TMA.
 static int launch_attention_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                        const int* seq_start, const int* seq_pos0, const int* seq_slot, const int* page_table,
                        int max_pages, int page_size, void* out, int n_tokens, int n_seqs, int max_new,
                        int n_heads, int n_kv_heads, int head_dim, int window, float scale, int splits,
                        float* scratch, long scratch_floats, cudaStream_t stream, int n_pages = 0,
-                       int* status = nullptr) {
+                       int* status = nullptr, const FusedRotary* fz = nullptr) {
     MDMA_REQUIRE(attention_mma_supported(n_heads, n_kv_heads, head_dim),
                  "attention_mma: heads %d / kv heads %d / head_dim %d is outside its limits (head_dim a multiple of 16 up to 128, group up to 64)",
                  n_heads, n_kv_heads, head_dim);
@@ -775,6 +875,18 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
     p.group = n_heads / n_kv_heads; p.tile_tokens = kRows / p.group; p.window = window; p.splits = splits;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.part_o = nullptr; p.part_ml = nullptr; p.status = status;
+    p.rot_inv_freq = nullptr; p.rotary_dim = 0; p.rot_interleaved = 0;
+    p.proj_partial = nullptr; p.proj_splits = 0; p.proj_split_stride = 0; p.proj_width = 0;
+    p.k_cache_w = nullptr; p.v_cache_w = nullptr;
+    if (fz != nullptr) {
+        MDMA_REQUIRE(max_new == 1 && n_pages > 0 && attention_fused_rotary_supported(n_heads, n_kv_heads, head_dim, page_size, fz->rotary_dim),
+                     "attention: the rotary encoding can be done inside the kernel only for single tokens, page sizes that are multiples of 32 and groups up to 16");
+        MDMA_REQUIRE(fz->inv_freq && (fz->splits == 0 || fz->partial), "attention: the fused rotary encoding needs its frequency table (and the partial sums it names)");
+        p.rot_inv_freq = fz->inv_freq; p.rotary_dim = fz->rotary_dim; p.rot_interleaved = fz->interleaved;
+        p.proj_partial = fz->partial; p.proj_splits = fz->partial ? fz->splits : 0;
+        p.proj_split_stride = fz->split_stride; p.proj_width = fz->width;
+        p.k_cache_w = (__nv_bfloat16*)const_cast<void*>(k_cache); p.v_cache_w = (__nv_bfloat16*)const_cast<void*>(v_cache);
+    }
     if (splits > 1) {
         const long need = attention_mma_scratch_floats(n_tokens, n_heads, head_dim, splits);
         MDMA_REQUIRE(scratch && scratch_floats >= need, "attention_mma: %d splits need %ld floats of scratch, %ld given", splits, need, scratch_floats);
@@ -784,6 +896,7 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
     dim3 grid((max_new + p.tile_tokens - 1) / p.tile_tokens, n_seqs, n_kv_heads * splits);
     const bool tma_ok = n_pages > 0 && page_size % kDecodeKeys == 0 && ((uintptr_t)k_cache & 15) == 0 &&
                         ((uintptr_t)v_cache & 15) == 0;
+    MDMA_REQUIRE(fz == nullptr || tma_ok, "attention: the caches are not aligned for tile loads");
     if (max_new == 1 && p.group <= 16 && tma_ok) {
         // one token per sequence, tiles by TMA
         CUtensorMap mk, mv;
@@ -791,7 +904,7 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
         if (int rc = make_cache_map(&mv, v_cache, n_pages, page_size, n_kv_heads, head_dim, kDecodeKeys)) return rc;
         // eight warps when one block per (sequence, kv head) takes all keys, four when keys are split
         auto launch = [&](auto kernel, int nw, int dmax) -> int {
-            const int bytes = nw * 2 * kDecodeKeys * dmax * 2 + 16 * dmax * 2 + nw * 16 + 64;
+            const int bytes = nw * 2 * kDecodeKeys * dmax * 2 + 16 * dmax * 2 + nw * 16 + 64 + 8 * dmax;
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
             if (e != cudaSuccess) return fail("attention: cannot reserve %d bytes of shared memory: %s", bytes, cudaGetErrorString(e));
             e = launch_chained(kernel, grid, dim3(nw * 32), bytes, stream, mk, mv, p);
@@ -803,11 +916,21 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
         int sm_count = 0, dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        const bool wide = splits == 1 && (long)n_seqs * n_kv_heads < 2l * sm_count;
-        if (wide && head_dim <= 64) rc = launch(attention_decode_tma_kernel<64, kDecodeKeys, 8>, 8, 64);
-        else if (wide) rc = launch(attention_decode_tma_kernel<128, kDecodeKeys, 8>, 8, 128);
-        else if (head_dim <= 64) rc = launch(attention_decode_tma_kernel<64, kDecodeKeys, 4>, 4, 64);
-        else rc = launch(attention_decode_tma_kernel<128, kDecodeKeys, 4>, 4, 128);
+        // the most warps per block with which every block of the grid is resident at once
+        const long blocks = (long)n_seqs * n_kv_heads * splits;
+        const int nw = blocks <= sm_count ? 8 : blocks <= 3l * sm_count ? 4 : blocks <= 4l * sm_count ? 3 :
+                       blocks <= 5l * sm_count ? 2 : 4;
+        if (head_dim <= 64) {
+            rc = nw == 8 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 8>, 8, 64)
+               : nw == 4 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 4>, 4, 64)
+               : nw == 3 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 3>, 3, 64)
+                         : launch(attention_decode_tma_kernel<64, kDecodeKeys, 2>, 2, 64);
+        } else {
+            rc = nw == 8 ? launch(attention_decode_tma_kernel<128, kDecodeKeys, 8>, 8, 128)
+               : nw == 4 ? launch(attention_decode_tma_kernel<128, kDecodeKeys, 4>, 4, 128)
+               : nw == 3 ? launch(attention_decode_tma_kernel<128, kDecodeKeys, 3>, 3, 128)
+                         : launch(attention_decode_tma_kernel<128, kDecodeKeys, 2>, 2, 128);
+        }
         if (rc) return rc;
     } else if (max_new == 1 && p.group <= 16) {
         // one token per sequence: the decode kernel (no padding rows beyond one 16-row tile)

@@ -449,14 +449,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             if (sg.kind == kSegTail) {
                 // the pair before this one did the first K blocks of this tile: wait for its partial sums
                 const volatile int* flag = p.sk_flags + (size_t)(pair - 1) * 2 + rank;
-                const uint64_t t_start = ptx::global_timer_ns();
-                bool there = false;
-                for (uint32_t spin = 0;; ++spin) {
-                    int v;
-                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-                    if (v != 0) { there = true; break; }
-                    if ((spin & 63u) == 63u && (*abort_flag || ptx::global_timer_ns() - t_start > ptx::kWaitLimitNs)) break;
-                }
+                const bool there = ptx::flag_wait(flag, abort_flag);
                 ok = __all_sync(0xffffffffu, there);
                 if (!ok) { *abort_flag = 1; break; }
             }
@@ -556,6 +549,30 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     if (MODE == kTcAccumulate) reinterpret_cast<float*>(out)[t * ldo + f] += acc;
     else if (out_f32) reinterpret_cast<float*>(out)[t * ldo + f] = acc;
     else reinterpret_cast<__nv_bfloat16*>(out)[t * ldo + f] = __float2bfloat16_rn(acc);
+}
+
+// A kernel that does nothing but wait, with the waits of the kernels above: mode 0 on an mbarrier that
+// nobody arrives on, mode 1 on a flag in global memory.  With a flag that nothing sets the wait runs out
+// after the limit, the block raises its abort flag and reports through the status word, as a product
+// kernel whose protocol broke would: this is how the tests see that path without breaking anything.
+__global__ void wait_probe_kernel(int mode, const int* flag, int* status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_addr(&bar), 1);
+        abort_word = 0;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x < 32) {
+        ok = mode == 0 ? ptx::mbar_wait(ptx::smem_addr(&bar), 0, abort_flag) : ptx::flag_wait(flag, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) *abort_flag = 1;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, 5);
 }
 
 // ---- tensor maps ----------------------------------------------------------
@@ -729,6 +746,22 @@ static int run_tc_bn(int bn, const void* x, int ldx, const void* w, const void* 
 extern "C" {
 
 const char* mdma_last_error() { return error_buffer(); }
+
+// The wall-clock limit of every bounded wait of the kernels in this source (2 s unless changed).
+int mdma_set_wait_limit_ns(unsigned long long ns) {
+    MDMA_REQUIRE(ns > 0, "set_wait_limit: the limit must be positive");
+    cudaError_t e = cudaMemcpyToSymbol(ptx::g_wait_limit_ns, &ns, sizeof(ns));
+    if (e != cudaSuccess) return fail("set_wait_limit: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+// Launches the kernel that only waits (see wait_probe_kernel): mode 0 an mbarrier, mode 1 the flag.
+int mdma_wait_probe(int mode, const int* flag, int* status, cudaStream_t stream) {
+    MDMA_REQUIRE((mode == 0 || mode == 1) && status && (mode == 0 || flag), "wait_probe: bad arguments");
+    wait_probe_kernel<<<1, 64, 0, stream>>>(mode, flag, status);
+    MDMA_LAUNCH_OK("wait_probe");
+    return 0;
+}
 
 // Returns 1 if the tensor-core kernel takes this weight shape.
 int mdma_gemm_tc_supported(int n_features, int K) { return (K % 8 == 0 && K >= 8 && n_features >= 1) ? 1 : 0; }

@@ -43,6 +43,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
+// The limit the waits of this file's kernels use: the constant above unless the host changed it (each
+// library source has its own copy; a test shortens the one of the matrix-product kernels to see a wait
+// run out in milliseconds on a flag that nothing sets).
+static __device__ unsigned long long g_wait_limit_ns = kWaitLimitNs;
 
 // Waits for the phase `parity` of `bar`.  Returns false if the block aborted or
 // the limit ran out (then the abort flag is raised).
@@ -53,8 +57,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+            if (global_timer_ns() - t0 > g_wait_limit_ns) { *abort_flag = 1; return false; }
         }
+    }
+}
+
+// Waits until the integer at `flag` (global memory, written by another block with release semantics) is
+// not zero.  Returns false if the block aborted or the limit ran out; the caller raises the abort flag.
+__device__ __forceinline__ bool flag_wait(const volatile int* flag, volatile int* abort_flag) {
+    const uint64_t t_start = global_timer_ns();
+    for (uint32_t spin = 0;; ++spin) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v != 0) return true;
+        if ((spin & 63u) == 63u && (*abort_flag || global_timer_ns() - t_start > g_wait_limit_ns)) return false;
     }
 }
 

@@ -34,6 +34,7 @@ def scratch_floats_bound(sms: int, max_tokens: int, max_seqs: int, attention_sha
     need = 2 * sms * 128 * 64
     if max_tokens > PAIR_TOKENS:
         need = max(need, pair_scratch_floats(sms))
+    products, need = need, 0          # a projection's partial sums and the attention's can be alive together
     for heads, kv_heads, head_dim in attention_shapes:
         group = max(1, heads // max(kv_heads, 1))
         # Keys are split only while the grid is short of blocks (see `attention_splits`): decode has
@@ -42,7 +43,7 @@ def scratch_floats_bound(sms: int, max_tokens: int, max_seqs: int, attention_sha
         # splits <= 2 x SMs / blocks + 1, so tokens x splits < 4 x SMs x tile tokens / kv heads.
         tile_tokens = max(1, 64 // group)
         need = max(need, 5 * sms * group * (head_dim + 2), 4 * sms * tile_tokens * group * (head_dim + 2))
-    return need
+    return products + need + 64
 
 
 class TensorState:
@@ -199,7 +200,7 @@ def attention_splits(n_seqs: int, max_new: int, max_len: int, n_heads: int, n_kv
         # decode kernel: a block's warps each take 32-key tiles in turn.  Short contexts: one block of
         # eight warps per (sequence, kv head), no merge kernel; else four warps and a K split.
         blocks = n_seqs * n_kv_heads
-        if max_len <= 1024 or blocks >= 2 * sms:
+        if max_len <= 1024 or blocks >= sms:
             return 1
         rounds = -(-max_len // (32 * 4))           # four warps x 32 keys per round
         return max(2, min(-(-3 * sms // blocks), rounds, 32))
@@ -257,3 +258,57 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
           _i(ctx.max_new), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(window), _f(scale), _i(splits),
           _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status), _stream(),
           launches=2 if splits > 1 else 1)
+
+
+def fused_rotary_supported(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, rotary_dim: int) -> bool:
+    """Whether single-token steps of this geometry can rotate q and k and write the cache inside the
+    attention kernel (`attention_decode_rotary`)."""
+    return (attention_supported(n_heads, n_kv_heads, head_dim) and n_heads // n_kv_heads <= 16
+            and page_size % 32 == 0 and rotary_dim % 2 == 0 and 2 <= rotary_dim <= head_dim)
+
+
+def attention_decode_rotary(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_kv_heads: int,
+                            head_dim: int, window: int, scale: float, inv_freq: torch.Tensor, rotary_dim: int,
+                            interleaved: bool, splits: Optional[int] = None, st: Optional[TensorState] = None) -> None:
+    """A step of one token per sequence: the projection rows `qkv` (or the K-split partial sums a
+    deferred product left for them) are rotated, the keys and values written to the cache and the
+    attention computed by ONE kernel; it asks for all its key and value tiles before it waits for
+    the projection, because it takes the token's own key and value from registers, not from the cache."""
+    _need_cuda(qkv, view.k, view.v, out, view.page_table, inv_freq)
+    if qkv.dtype != torch.bfloat16 or view.k.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention takes bfloat16")
+    assert qkv.stride(1) == 1 and out.is_contiguous() and out.shape[1] == n_heads * head_dim
+    assert view.k.is_contiguous() and view.v.is_contiguous() and inv_freq.dtype == torch.float32
+    assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim and ctx.max_new == 1
+    st = st or _device_state(qkv.device)
+    pend = take_pending(qkv, ops.GEMM_STORE, ctx.n_tokens, st)
+    partial, proj_splits, stride = (None, 0, 0)
+    if pend is not None:
+        partial, proj_splits, stride = pend
+    else:
+        flush_pending(qkv.device, st)
+    if splits is None:
+        splits = attention_splits(ctx.n_seqs, 1, ctx.max_len, n_heads, n_kv_heads, st.sms)
+    # the attention's own partials (keys split over blocks) lie behind the projection's
+    used = -(-proj_splits * stride // 64) * 64
+    need = ctx.n_tokens * n_heads * splits * (head_dim + 2) if splits > 1 else 0
+    st.need(used + need, "attention over split keys")
+    own = st.scratch[used:]
+    _call("tensor", "mdma_attention_decode_rotary", _ptr(qkv), _i(qkv.stride(0)), _ptr(partial), _i(proj_splits),
+          ctypes.c_long(stride), _ptr(inv_freq), _i(rotary_dim), _i(int(interleaved)), _ptr(view.k), _ptr(view.v),
+          _i(view.k.shape[0]), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
+          _i(view.max_pages), _i(view.page_size), _ptr(out), _i(ctx.n_seqs), _i(n_heads), _i(n_kv_heads), _i(head_dim),
+          _i(window), _f(scale), _i(splits), _ptr(own), ctypes.c_long(own.numel()), _ptr(st.status), _stream(),
+          launches=2 if splits > 1 else 1)
+
+
+def set_wait_limit(seconds: float) -> None:
+    """The wall-clock limit of the bounded waits in the matrix-product kernels (2 s by default)."""
+    _call("tensor", "mdma_set_wait_limit_ns", ctypes.c_ulonglong(int(seconds * 1e9)), launches=0)
+
+
+def wait_probe(mode: int, flag: torch.Tensor, st: Optional[TensorState] = None) -> None:
+    """Launch the kernel that only waits, on an mbarrier nobody arrives on (mode 0) or on `flag` (mode 1),
+    with the product kernels' own wait routines; a wait that runs out sets the status word."""
+    st = st or _device_state(flag.device)
+    _call("tensor", "mdma_wait_probe", _i(mode), _ptr(flag), _ptr(st.status), _stream())

@@ -11,6 +11,8 @@ writes nothing.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -97,8 +99,17 @@ class Attention(Part):
         n = ctx.n_tokens
         qkv = ctx.buf("qkv", self.row_width)
         out = ctx.buf("attn_out", self.q_width)
-        self.qkv_proj.store(h, qkv, n, defer=getattr(self.position, "fuses_pending", False))
         write = owns_cache and not self.shared_cache
+        if write and ctx.max_new == 1 and self._fast_ok and self._fusable(ctx, view):
+            # single tokens: the attention kernel rotates q and k and writes the cache itself
+            from .. import ops_tensor
+            inv_freq, rotary_dim, interleaved = self.position.rotary_table()
+            self.qkv_proj.store(h, qkv, n, defer=True)
+            ops_tensor.attention_decode_rotary(ctx, qkv, view, out, self.n_heads, self.n_kv_heads, self.head_dim,
+                                               self.window, self.scale, inv_freq, rotary_dim, interleaved, st=self.rt.tc)
+            self.o_proj.accumulate(out, x, n)
+            return
+        self.qkv_proj.store(h, qkv, n, defer=getattr(self.position, "fuses_pending", False))
         self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, view, write)
         if self.rt.attention == "fast" and self._fast_ok:
             from .. import ops_tensor
@@ -112,6 +123,20 @@ class Attention(Part):
                                  view.page_table, view.max_pages, view.page_size, out,
                                  self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
         self.o_proj.accumulate(out, x, n)
+
+    def _fusable(self, ctx, view) -> bool:
+        """Whether this step's attention kernel should do the position encoding and the cache write
+        itself.  It pays while every (sequence, kv head) has a block of eight warps to itself (measured at
+        the 8B layer shape: the chain of a layer takes 93.6 us against 96.4 us at batch 8, but 139 us
+        against 135 us at batch 64, where each of many small blocks repeats the work on the projection
+        row).  MDMA_FUSED_ROTARY=0 turns it off, for comparisons."""
+        if self.rt.attention != "fast" or not hasattr(self.position, "rotary_table") or os.environ.get("MDMA_FUSED_ROTARY") == "0":
+            return False
+        from .. import ops_tensor
+        sms = self.rt.tc.sms if self.rt.tc is not None else 0
+        return (ctx.n_seqs * self.n_kv_heads <= sms and
+                ops_tensor.fused_rotary_supported(self.n_heads, self.n_kv_heads, self.head_dim, view.page_size,
+                                                  self.position.rotary_table()[1]))
 
     def resident_tensors(self):
         return [self.qkv_proj.w, self.o_proj.w]

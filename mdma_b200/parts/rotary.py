@@ -70,6 +70,11 @@ class Rotary(Part):
     def device_tensors(self):
         return {"inv_freq": ((self.rotary_dim // 2,), torch.float32)}
 
+    def rotary_table(self):
+        """(inverse frequencies on the device, rotated width, interleaved?): what a mixer needs to do this
+        encoding inside a kernel of its own instead of calling `encode_and_store`."""
+        return self.inv_freq, self.rotary_dim, self.interleaved
+
     def encode_and_store(self, ctx, qkv, n_heads, n_kv_heads, head_dim, view, write_kv):
         partial, splits, stride = None, 0, 0
         if self.rt.gemm == "tensor":

@@ -316,3 +316,32 @@ def test_logits_of_the_replayed_decode_step_match_the_oracle():
         for s in slots:
             eng.release(s)
         del eng
+
+
+def test_generation_reports_a_kernel_that_gave_up():
+    """The status word that a bounded wait sets travels to the host with every step's tokens; generation
+    raises instead of handing out tokens of a step that is not valid, gives its slots back, and the
+    next call is clean."""
+    from mdma_b200.engine import Engine
+    from mdma_b200.engine.generate import Generator
+    from mdma_b200.ops import KernelError
+    d, c, tensors = make_model(TINY_B, 1, torch.bfloat16, std_scale=SHARP)
+    eng = Engine(d, dtype="bfloat16", max_batch=2, max_context=128)
+    p = prompts_for(TINY_B, (6, 9), 3)
+    want = [o.tokens for o in eng.generate(p, max_tokens=12)]
+    eng.rt.tc.status[0] = 3                         # as a block of a product kernel would
+    with pytest.raises(KernelError, match="wait limit"):
+        eng.generate(p, max_tokens=12)
+    assert not eng.cache.lengths and int(eng.rt.tc.status[0]) == 0
+    assert [o.tokens for o in eng.generate(p, max_tokens=12)] == want
+    # during the replayed steps too: the word is read with each run's tokens
+    calls = []
+
+    def poison_once(request, token):
+        calls.append(token)
+        if len(calls) == 8:
+            eng.rt.tc.status[0] = 1
+    with pytest.raises(KernelError, match="wait limit"):
+        Generator(eng).generate(p, 40, on_token=poison_once)
+    assert not eng.cache.lengths
+    assert [o.tokens for o in eng.generate(p, max_tokens=12)] == want

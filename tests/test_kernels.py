@@ -300,15 +300,15 @@ class StepMeta:
 
 @pytest.mark.parametrize("H,K,hd,window", [(8, 2, 128, 0), (6, 2, 48, 0), (4, 4, 16, 0), (12, 2, 64, 0),
                                            (6, 1, 80, 0), (8, 2, 128, 100), (5, 5, 112, 33), (32, 8, 128, 0)])
-@pytest.mark.parametrize("case", ["prefill", "chunked", "decode", "decode_split", "decode_long", "decode_many",
-                                  "decode_page16", "prefill_tc", "chunked_tc"])
+@pytest.mark.parametrize("case", ["prefill", "chunked", "decode", "decode_split", "decode_long", "decode_many1",
+                                  "decode_many3", "decode_many4", "decode_page16", "prefill_tc", "chunked_tc"])
 @pytest.mark.parametrize("poison", [False, True])
 def test_attention_tensor(H, K, hd, window, case, poison):
     """The tensor-core attention against the float64 statement of the reference's loop:
     whole prompts, prompts on top of a cached prefix, single tokens (one block of eight warps; keys
     split over blocks, by hand and by the kernel's own choice for a long context; so many sequences
-    that blocks of four warps are taken; pages that the tile loads cannot use), with and without NaN in
-    every cache row that belongs to nobody."""
+    that blocks of four, three and two warps are taken; pages that the tile loads cannot use), with and
+    without NaN in every cache row that belongs to nobody."""
     from mdma_b200 import ops_tensor
     torch.manual_seed(H * 1000 + hd)
     page = 16 if case == "decode_page16" else 64
@@ -320,11 +320,11 @@ def test_attention_tensor(H, K, hd, window, case, poison):
         cached, new = [70, 129, 1], [100, 20, 64]
     elif case == "decode_long":
         cached, new = [2500, 1030, 7], [1, 1, 1]          # beyond 1024: the kernel splits the keys itself
-    elif case == "decode_many":
+    elif case.startswith("decode_many"):
         sms = torch.cuda.get_device_properties(0).multi_processor_count
-        n = -(-2 * sms // K) + 1                          # sequences x kv heads >= 2 x SMs: four-warp blocks, no split
+        n = -(-int(case[-1]) * sms // K) + 1              # sequences x kv heads just beyond 1, 3, 4 x SMs: blocks of 4, 3, 2 warps
         g = torch.Generator().manual_seed(7)
-        cached, new = torch.randint(0, 200, (n,), generator=g).tolist(), [1] * n
+        cached, new = torch.randint(0, 150, (n,), generator=g).tolist(), [1] * n
     else:
         cached, new = [299, 0, 64, 1000], [1, 1, 1, 1]
     lens = [c + n for c, n in zip(cached, new)]
@@ -346,6 +346,76 @@ def test_attention_tensor(H, K, hd, window, case, poison):
                                scale, window)
     close(out[:T], want, 2e-2, 2e-2)
     assert bool((out[T:] == 9.0).all())
+
+
+@pytest.mark.parametrize("H,K,hd,rot,layout,window", [(8, 2, 128, 128, "split_half", 0), (6, 2, 48, 48, "interleaved", 0),
+                                                       (4, 4, 16, 16, "split_half", 0), (12, 2, 64, 32, "split_half", 70),
+                                                       (32, 8, 128, 128, "split_half", 0), (5, 5, 112, 64, "interleaved", 33)])
+@pytest.mark.parametrize("proj_splits,key_splits", [(0, None), (4, None), (3, 3), (0, 4)])
+def test_attention_decode_with_the_rotary_encoding_inside(H, K, hd, rot, layout, window, proj_splits, key_splits):
+    """Single tokens: one kernel sums the projection's partial rows, rotates q and k, writes k and v to the
+    cache and attends.  Against the separate rotary kernel (the same cache rows, bit for bit) and against
+    the float64 statement of rotation and attention; the cache starts with NaN in every row nobody owns."""
+    from mdma_b200 import ops_tensor
+    from mdma_b200.parts.rotary import inverse_frequencies
+    ops = ops_mod()
+    torch.manual_seed(H * 100 + hd + proj_splits)
+    page = 64
+    cached = [299, 0, 64, 1000, 31]
+    B = len(cached)
+    lens = [c + 1 for c in cached]
+    kc, vc, table, max_pages, dense = fill_cache(lens, K, hd, page, torch.bfloat16, seed=hd, poison=True)
+    width = (H + 2 * K) * hd
+    inv_freq = inverse_frequencies(rot, 10000.0).to(DEV)
+    rows = torch.randn(B, width)
+    if proj_splits:
+        parts = torch.randn(proj_splits, B, width) * 0.5
+        parts[-1] = rows - parts[:-1].sum(0)
+        total = torch.zeros(B, width)
+        for sidx in range(proj_splits):                       # the kernels' order of summation
+            total = total + parts[sidx]
+        rows = total
+    qkv = rows.bfloat16().to(DEV)                             # read only when there are no partial sums
+    meta = StepMeta(cached, [1] * B)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    tok_seq, tok_pos = i32(list(range(B))), i32(cached)
+    # the separate kernel on copies: rotated q in its buffer, k and v in its caches
+    kc2, vc2, qkv2 = kc.clone(), vc.clone(), qkv.clone()
+    part_dev = parts.to(DEV).contiguous() if proj_splits else None
+    ops.rope_cache_write(qkv2, B, tok_seq, tok_pos, meta.seq_slot, inv_freq, kc2, vc2, table, max_pages, page, H, K, hd,
+                         rot, layout == "interleaved", True, part_dev, proj_splits, B * width)
+
+    class View:
+        pass
+    view = View()
+    view.k, view.v, view.page_table, view.max_pages, view.page_size = kc, vc, table, max_pages, page
+    out = torch.full((B + 1, H * hd), 9.0, device=DEV, dtype=torch.bfloat16)
+    st = ops_tensor._device_state(torch.device(DEV))
+    if proj_splits:
+        st.need(proj_splits * B * width, "test")
+        st.scratch[:proj_splits * B * width].copy_(part_dev.reshape(-1))
+        st.pending = ops_tensor.Pending(qkv, ops.GEMM_STORE, proj_splits, B, width)
+    scale = 1.0 / math.sqrt(hd)
+    ops_tensor.attention_decode_rotary(meta, qkv, view, out, H, K, hd, window, scale, inv_freq, rot,
+                                       layout == "interleaved", splits=key_splits)
+    ops_tensor.check_status(torch.device(DEV))
+    # the cache rows of the new tokens, and nothing else, were written: exactly what the separate kernel writes
+    assert torch.equal(kc.view(torch.int16), kc2.view(torch.int16)) and torch.equal(vc.view(torch.int16), vc2.view(torch.int16))
+    # attention over the (now complete) sequences, in float64, with the rotated queries of the separate kernel
+    for sidx, n in enumerate(lens):
+        kd, vd = dense[sidx]
+        pg = int(table[sidx, (n - 1) // page])
+        kd[n - 1], vd[n - 1] = kc2[pg, (n - 1) % page].cpu(), vc2[pg, (n - 1) % page].cpu()
+    q = qkv2[:, :H * hd].double().cpu().reshape(B, H, hd)
+    want = reference_attention(q, dense, list(range(B)), cached, scale, window)
+    close(out[:B], want, 2e-2, 2e-2)
+    assert bool((out[B:] == 9.0).all())
+    # and the rotation itself against the plain statement
+    from plain_llama import plain_rope
+    for sidx in range(B):
+        qr = plain_rope(rows[sidx, :H * hd].double().reshape(1, H, hd)[..., :rot], torch.tensor([cached[sidx]]),
+                        inv_freq.cpu(), layout)
+        close(qkv2[sidx, :H * hd].reshape(H, hd)[:, :rot], qr[0], 2e-2, 1e-2)
 
 
 @pytest.mark.parametrize("path", ["decode", "decode_split", "prefill_tc", "chunked_tc", "chunked_mma"])
@@ -646,3 +716,40 @@ def test_sample_follows_the_distribution(impl):
     freq = torch.bincount(tok.long().cpu(), minlength=vocab).double() / n
     p = torch.softmax(row.double(), 0)
     assert (freq - p).abs().max() < 4 * (p.max() * (1 - p.max()) / n) ** 0.5 + 0.01
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_library_usable():
+    """Every wait of the tensor-core kernels has a limit; when it runs out the block gives up, the status
+    word is set and the host raises.  Seen here without breaking anything: the limit is shortened to
+    20 ms and a kernel that only waits (with the product kernels' wait routines) is given an mbarrier
+    that nobody arrives on, then a flag that nothing sets.  Afterwards the flags are clear and the next
+    product is right."""
+    import time
+    from mdma_b200 import ops_tensor
+    ops = ops_mod()
+    dev = torch.device(DEV)
+    st = ops_tensor._device_state(dev)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops_tensor.set_wait_limit(0.02)
+    try:
+        for mode in (0, 1):
+            st.sk_flags[3] = 1                      # as a block pair that gave up would leave it
+            t0 = time.perf_counter()
+            ops_tensor.wait_probe(mode, flag)
+            torch.cuda.synchronize()
+            assert time.perf_counter() - t0 < 1.0   # it gave up after the short limit, not after 2 s
+            with pytest.raises(ops.KernelError, match="wait limit"):
+                ops_tensor.check_status(dev)
+            assert int(st.status[0]) == 0 and int(st.sk_flags.sum()) == 0
+            ops_tensor.check_status(dev)            # and stays quiet
+        flag.fill_(1)                               # a flag that IS set: the wait ends at once, nothing is reported
+        ops_tensor.wait_probe(1, flag)
+        ops_tensor.check_status(dev)
+    finally:
+        ops_tensor.set_wait_limit(2.0)
+    a = torch.randn(5, 256, device=DEV).bfloat16()
+    w = torch.randn(130, 256, device=DEV).bfloat16()
+    out = torch.zeros(5, 130, device=DEV, dtype=torch.bfloat16)
+    ops_tensor.gemm(a, w, out)
+    ops_tensor.check_status(dev)
+    close(out, a.double().cpu() @ w.double().cpu().t(), 0.2, 2e-2)
