@@ -107,7 +107,9 @@ class DecodeSession:
     def _draws(self) -> bool:
         return not self.params.is_greedy
 
-    def _body(self, B: int, draws: bool) -> None:
+    def set_context(self, B: int) -> StepContext:
+        """The step context of one token for each of the first B live sequences, read from the
+        session's device buffers (what the captured step sees)."""
         ctx = self.ctx
         ctx.ids, ctx.tok_pos, ctx.seq_slot, ctx.seq_pos0 = self.ids[:B], self.tok_pos[:B], self.seq_slot[:B], self.seq_pos0[:B]
         ctx.tok_seq, ctx.seq_start, ctx.want_rows = self.arange[:B], self.arange[:B + 1], self.arange[:B]
@@ -115,6 +117,10 @@ class DecodeSession:
         ctx.max_new, ctx.max_len = 1, self._bucket
         ctx.decode_only = True
         ctx.host_seq_new, ctx.host_seq_pos0, ctx.host_seq_slot = [1] * B, None, list(self.slots)
+        return ctx
+
+    def _body(self, B: int, draws: bool) -> None:
+        ctx = self.set_context(B)
         self.engine.model.forward(ctx, self.engine.cache, self.logits[:B])
         s = self.sampler
         if draws:

@@ -35,3 +35,28 @@ def test_shapes_are_those_of_one_architecture():
         c = LlamaConfig.from_dict(cfg)            # every shape is a valid configuration of the architecture
         assert c.num_attention_heads % c.num_key_value_heads == 0 and label
     assert bench.SHAPES["llama-3.1-8b"][1]["num_hidden_layers"] == 32
+
+
+def test_kernel_times_parses_its_options():
+    r = subprocess.run([sys.executable, "-m", "mdma_b200.kernel_times", "--help"], capture_output=True, text=True,
+                       cwd=ROOT, timeout=120)
+    assert r.returncode == 0 and "--context" in r.stdout and "--copies" in r.stdout
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_kernel_times_runs_on_the_engines_own_parts():
+    """The per-kernel timing tool still runs (it drives the engine's parts and decode session, so a change
+    to them shows here), on a tiny shape, with and without the rotary encoding inside the attention kernel."""
+    args = ["--hidden", "128", "--intermediate", "144", "--heads", "4", "--kv-heads", "2", "--head-dim", "32",
+            "--vocab", "200", "--batch", "3", "--context", "100", "--copies", "2", "--repeat", "4"]
+    for env in ({}, {"MDMA_FUSED_ROTARY": "0"}):
+        r = subprocess.run([sys.executable, "-m", "mdma_b200.kernel_times", *args], capture_output=True, text=True,
+                           cwd=ROOT, timeout=600, env=dict(os.environ, **env))
+        assert r.returncode == 0, r.stderr
+        for line in ("RMSNorm", "QKV product", "attention", "O product", "gate+up", "down product",
+                     "the layer as the engine runs it", "final norm + LM head", "argmax", "sample"):
+            assert any(l.startswith(line) or line in l for l in r.stdout.splitlines()), (line, r.stdout)
+        assert ("(one kernel)" in r.stdout) == (not env)

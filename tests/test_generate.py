@@ -345,3 +345,21 @@ def test_generation_reports_a_kernel_that_gave_up():
         Generator(eng).generate(p, 40, on_token=poison_once)
     assert not eng.cache.lengths
     assert [o.tokens for o in eng.generate(p, max_tokens=12)] == want
+
+
+def test_an_engine_from_a_seed_holds_the_bits_of_the_folder_written_from_it():
+    """Seeded random weights are a function of (seed, tensor name, element): the device fills its arena with
+    the same bits that the folder writer produces on the host, so the same seed means the same model."""
+    from mdma_b200.engine import Engine, StepEntry
+    for cfg, seed, dtype in ((TINY_B, 5, "bfloat16"), (TINY_C, 6, "float32")):
+        wd = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+        d, c, tensors = make_model(cfg, seed, wd, std_scale=SHARP)
+        from_seed = Engine(config=cfg, seed=seed, dtype=dtype, max_batch=2, max_context=64, init_std=0.02 * SHARP)
+        from_folder = Engine(d, dtype=dtype, max_batch=2, max_context=64)
+        a = [t for p in from_seed.model.all_parts() for t in p.resident_tensors()]
+        b = [t for p in from_folder.model.all_parts() for t in p.resident_tensors()]
+        assert len(a) == len(b) and all(torch.equal(x, y) for x, y in zip(a, b))
+        ids = prompts_for(cfg, (20,), 1)[0]
+        la = from_seed.step([StepEntry(from_seed.acquire(), ids, [19])]).clone()
+        lb = from_folder.step([StepEntry(from_folder.acquire(), ids, [19])])
+        assert torch.equal(la, lb)

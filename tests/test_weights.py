@@ -111,3 +111,36 @@ def test_sharded_folder(tmp_path):
     json.dump({"weight_map": wm}, open(os.path.join(d, "model.safetensors.index.json"), "w"))
     loaded = load_tensors(d, expected_of(TINY_A), torch.float32)
     assert all(torch.equal(loaded[n], tensors[n]) for n in names)
+
+
+def test_the_container_agrees_with_the_safetensors_package(tmp_path):
+    """The folder writer and the reader of this library against the `safetensors` package (a file-format
+    library, not model code): it reads what we write, we read what it writes, tensor for tensor."""
+    st = pytest.importorskip("safetensors.torch")
+    d, _, tensors = make_model(TINY_B, 1, torch.bfloat16)
+    theirs = st.load_file(os.path.join(d, "model.safetensors"))
+    assert set(theirs) == set(tensors)
+    for k, v in tensors.items():
+        assert theirs[k].dtype == v.dtype and torch.equal(theirs[k], v), k
+    t = {"w": torch.randn(5, 7), "b": torch.randn(9).bfloat16(), "i": torch.arange(12, dtype=torch.int32).reshape(3, 4)}
+    path = str(tmp_path / "theirs.safetensors")
+    st.save_file(t, path)
+    f = SafetensorsFile(path)
+    for k, v in t.items():
+        assert torch.equal(f.tensor(k), v) and f.tensor(k).dtype == v.dtype
+
+
+def test_seeded_weights_do_not_depend_on_the_order_or_the_piece(tmp_path):
+    """Element i of a tensor is a function of (seed, name, i): a tensor made alone, in pieces, or as part of a
+    model has the same values (the device fills with the same arithmetic; a GPU test compares the bits)."""
+    from mdma_b200.spec import TensorSpec
+    from mdma_b200.weights.random_init import normal_values, random_tensor, tensor_key
+    _, _, t = make_model(TINY_A, 7, torch.float32)
+    name = "model.layers.1.mlp.down_proj.weight"
+    alone = random_tensor(name, TensorSpec(tuple(t[name].shape)), 7, torch.float32)
+    assert torch.equal(alone, t[name])
+    key = tensor_key(7, name)
+    whole = normal_values(key, 0, 1000, 0.02)
+    pieces = [normal_values(key, lo, 250, 0.02) for lo in range(0, 1000, 250)]
+    assert (whole == __import__("numpy").concatenate(pieces)).all()
+    assert torch.equal(torch.from_numpy(whole), t[name].flatten()[:1000])
