@@ -132,6 +132,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--prompt-len-range", type=int, nargs=2, default=None, metavar=("LO", "HI"),
+                    help="prompt lengths drawn uniformly from [LO, HI] instead of equal prompts (seeded)")
     ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES), help="layer sizes (default: the headline shape)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in config)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
@@ -170,7 +172,12 @@ def main() -> int:
     gen = torch.Generator().manual_seed(0)
 
     def prompts(n, length):
-        return [torch.randint(0, cfg["vocab_size"], (length,), generator=gen).tolist() for _ in range(n)]
+        if args.prompt_len_range is not None and length == args.prompt_len:
+            lo, hi = args.prompt_len_range
+            lens = torch.randint(lo, hi + 1, (n,), generator=gen).tolist()
+        else:
+            lens = [length] * n
+        return [torch.randint(0, cfg["vocab_size"], (m,), generator=gen).tolist() for m in lens]
 
     def time_decode(batch, steps):
         """Device time of `steps` decode steps of `batch` sequences after prompt_len-token prompts."""
@@ -192,10 +199,10 @@ def main() -> int:
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
         per_graph = sess.launches_per_step
-        ctx_now = args.prompt_len + warmup + steps
+        mean_prompt = sum(len(p) for p in ps) / batch
         for s in slots:
             eng.release(s)
-        return ms / steps, per_graph * steps, ctx_now
+        return ms / steps, per_graph * steps, mean_prompt
 
     def time_prefill(T=args.prefill_tokens):
         times = []
@@ -222,9 +229,10 @@ def main() -> int:
 
     clock = ClockSampler()          # samples until every measurement of this run is done
     clock.start()
-    ms_step, launches, ctx_end = time_decode(args.batch, args.steps)
+    ms_step, launches, mean_prompt = time_decode(args.batch, args.steps)
     value = args.batch * 1000.0 / ms_step
-    avg_ctx = args.prompt_len + warmup + args.steps / 2
+    ctx_end = int(mean_prompt) + warmup + args.steps
+    avg_ctx = mean_prompt + warmup + args.steps / 2
     bytes_step = decode_bytes(cfg, args.layers, args.batch, avg_ctx)
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
 
@@ -253,7 +261,9 @@ def main() -> int:
                "with_prompt_step": round(args.batch * len(stamps) / (stamps[-1] - t_start), 2)}
 
     out = {
-        "metric": f"decode tokens/s ({shape_name}, batch {args.batch}, after {args.prompt_len}-token prompts)",
+        "metric": f"decode tokens/s ({shape_name}, batch {args.batch}, after " + (
+            f"{args.prompt_len}-token prompts)" if args.prompt_len_range is None else
+            f"prompts of {args.prompt_len_range[0]}-{args.prompt_len_range[1]} tokens)"),
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (uniform random token ids, random N(0,0.02) weights)",

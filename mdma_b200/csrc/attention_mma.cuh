@@ -899,12 +899,14 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
     MDMA_REQUIRE(fz == nullptr || tma_ok, "attention: the caches are not aligned for tile loads");
     if (max_new == 1 && p.group <= 16 && tma_ok) {
         // one token per sequence, tiles by TMA
+        // heads of up to 64 elements take tiles of 64 keys when the pages allow: a tile of 32 such keys is
+        // 4 KB, too little for what a tile costs (the same 8 KB per tile as for heads of 128 then)
+        const int kb = (head_dim <= 64 && page_size % 64 == 0) ? 64 : kDecodeKeys;
         CUtensorMap mk, mv;
-        if (int rc = make_cache_map(&mk, k_cache, n_pages, page_size, n_kv_heads, head_dim, kDecodeKeys)) return rc;
-        if (int rc = make_cache_map(&mv, v_cache, n_pages, page_size, n_kv_heads, head_dim, kDecodeKeys)) return rc;
-        // eight warps when one block per (sequence, kv head) takes all keys, four when keys are split
+        if (int rc = make_cache_map(&mk, k_cache, n_pages, page_size, n_kv_heads, head_dim, kb)) return rc;
+        if (int rc = make_cache_map(&mv, v_cache, n_pages, page_size, n_kv_heads, head_dim, kb)) return rc;
         auto launch = [&](auto kernel, int nw, int dmax) -> int {
-            const int bytes = nw * 2 * kDecodeKeys * dmax * 2 + 16 * dmax * 2 + nw * 16 + 64 + 8 * dmax;
+            const int bytes = nw * 2 * kb * dmax * 2 + 16 * dmax * 2 + nw * 16 + 64 + 8 * dmax;
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
             if (e != cudaSuccess) return fail("attention: cannot reserve %d bytes of shared memory: %s", bytes, cudaGetErrorString(e));
             e = launch_chained(kernel, grid, dim3(nw * 32), bytes, stream, mk, mv, p);
@@ -920,7 +922,12 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
         const long blocks = (long)n_seqs * n_kv_heads * splits;
         const int nw = blocks <= sm_count ? 8 : blocks <= 3l * sm_count ? 4 : blocks <= 4l * sm_count ? 3 :
                        blocks <= 5l * sm_count ? 2 : 4;
-        if (head_dim <= 64) {
+        if (kb == 64) {
+            rc = nw == 8 ? launch(attention_decode_tma_kernel<64, 64, 8>, 8, 64)
+               : nw == 4 ? launch(attention_decode_tma_kernel<64, 64, 4>, 4, 64)
+               : nw == 3 ? launch(attention_decode_tma_kernel<64, 64, 3>, 3, 64)
+                         : launch(attention_decode_tma_kernel<64, 64, 2>, 2, 64);
+        } else if (head_dim <= 64) {
             rc = nw == 8 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 8>, 8, 64)
                : nw == 4 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 4>, 4, 64)
                : nw == 3 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 3>, 3, 64)

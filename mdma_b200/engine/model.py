@@ -63,10 +63,12 @@ class DecoderModel:
         return [self.blocks[e.layer].mixer.state_need() for e in self.spec.schedule]
 
     def workspace_columns(self) -> dict[str, tuple[int, str]]:
+        # the model's own: the residual stream and the normed rows the head reads; the rest is asked for by
+        # the block arrangements and the parts
         cols: dict[str, tuple[int, str]] = {"x": (self.spec.hidden_size, "f32"),
-                                             "normed": (self.spec.hidden_size, "act"),
                                              "h_rows": (self.spec.hidden_size, "act")}
-        for part in self.all_parts():
+        askers = [b for b in self.blocks if hasattr(b, "workspace")] + self.all_parts()
+        for part in askers:
             for name, (c, kind) in part.workspace().items():
                 old = cols.get(name)
                 if old is not None and old[1] != kind:
@@ -141,8 +143,13 @@ class DecoderModel:
         self.embedding.forward(ctx, ctx.ids, x)
         for n, entry in enumerate(self.spec.schedule):
             site = n if entry.cache is None else entry.cache
-            self.blocks[entry.layer].forward(ctx, x, cache.view(site, state_site=n),
-                                             owns_cache=entry.cache is None)
+            block = self.blocks[entry.layer]
+            if ctx.rt.gemm == "tensor" and not getattr(block, "handles_pending", False):
+                # a product of the block before may have left partial sums of x for a norm to add up; an
+                # arrangement that does not know of that gets x complete
+                from .. import ops_tensor
+                ops_tensor.flush_pending(x.device, ctx.rt.tc)
+            block.forward(ctx, x, cache.view(site, state_site=n), owns_cache=entry.cache is None)
         if ctx.rt.gemm == "tensor":
             from .. import ops_tensor
             ops_tensor.flush_pending(x.device, ctx.rt.tc)

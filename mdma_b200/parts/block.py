@@ -16,8 +16,14 @@ class PreNormBlock:
         self.ffn_norm = NORMS.get(spec.ffn_norm.kind)(spec.ffn_norm)
         self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn)
 
+    handles_pending = True      # completes x itself where a product left partial sums (see _settle)
+
     def parts(self):
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def workspace(self):
+        """Per-token workspace of the arrangement itself: name -> (columns, 'act' | 'f32')."""
+        return {"normed": (int(self.mixer_norm.params["width"]), "act")}
 
     def forward(self, ctx, x, view, owns_cache=True):
         h = ctx.buf("normed", x.shape[1])

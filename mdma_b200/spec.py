@@ -35,12 +35,15 @@ class PartSpec:
 
 @dataclass
 class LayerSpec:
-    """One layer's parts. `block` names the arrangement (registry BLOCKS)."""
+    """One layer's parts. `block` names the arrangement (registry BLOCKS).  An arrangement that has
+    more parts than these four (a norm on the queries and keys, norms after the mixer and the
+    feed-forward, a second feed-forward) finds them by name in `extras`."""
     block: str
     mixer_norm: PartSpec
     mixer: PartSpec
     ffn_norm: PartSpec
     ffn: PartSpec
+    extras: dict[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass

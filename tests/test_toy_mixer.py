@@ -318,3 +318,117 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path):
         out = eng.step([StepEntry(sl, [s[c + step]], [0]) for sl, s, c in zip(slots, seqs, cut)]).cpu().numpy()
         for row, (r, c) in enumerate(zip(ref, cut)):
             assert np.abs(out[row] - r[c + step]).max() < 5e-5
+
+
+# ---- a block arrangement of its own, with more parts than the four of a layer ------------------------------
+def register_toy_sandwich():
+    """x += post_norm(mixer(pre_norm(x))) and the same around the feed-forward: two norms per layer that the
+    built-in arrangement does not have, found in `LayerSpec.extras`; the arrangement asks for a workspace
+    buffer of its own.  Registered from here."""
+    from mdma_b200.config import Architecture
+    from mdma_b200.registry import ARCHITECTURES, BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+    from mdma_b200.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    class SandwichBlock:
+        def __init__(self, spec):
+            self.spec = spec
+            make = lambda reg, ps: reg.get(ps.kind)(ps)
+            self.mixer_norm, self.mixer = make(NORMS, spec.mixer_norm), make(MIXERS, spec.mixer)
+            self.ffn_norm, self.ffn = make(NORMS, spec.ffn_norm), make(FEED_FORWARDS, spec.ffn)
+            self.post_mixer, self.post_ffn = make(NORMS, spec.extras["post_mixer_norm"]), make(NORMS, spec.extras["post_ffn_norm"])
+
+        def parts(self):
+            return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.post_mixer, self.post_ffn]
+
+        def workspace(self):
+            return {"normed": (E, "act"), "branch": (E, "f32"), "branch_normed": (E, "act")}
+
+        def forward(self, ctx, x, view, owns_cache=True):
+            n = ctx.n_tokens
+            h, y, yn = ctx.buf("normed", E), ctx.buf("branch", E, torch.float32), ctx.buf("branch_normed", E)
+            for pre, part, post in ((self.mixer_norm, self.mixer, self.post_mixer), (self.ffn_norm, self.ffn, self.post_ffn)):
+                pre.forward(ctx, x, h)
+                y[:n].zero_()
+                if part is self.mixer:
+                    part.forward(ctx, h, y, view, owns_cache)
+                else:
+                    part.forward(ctx, h, y)
+                post.forward(ctx, y, yn)              # adds up what a K-split product left for y, then norms it
+                x[:n] += yn[:n].float()
+
+    BLOCKS.register("toy_sandwich", SandwichBlock, replace=True)
+
+    def describe(c):
+        norm = lambda prefix: PartSpec("rmsnorm", dict(width=E, eps=c["eps"]), prefix=prefix)
+        pos = PartSpec("rotary", dict(head_dim=D, rotary_dim=D, theta=c["theta"], layout="interleaved", scaling=None))
+        layers = []
+        for i in range(2):
+            p = f"l{i}."
+            layers.append(LayerSpec(
+                "toy_sandwich" if i == 0 else "prenorm", norm(p + "n1."),
+                PartSpec("attention", dict(hidden_size=E, num_heads=H, num_kv_heads=K, head_dim=D, scale=D ** -0.5,
+                                           window=0, position=pos), prefix=p + "attn."),
+                norm(p + "n2."), PartSpec("gated_mlp", dict(hidden_size=E, intermediate_size=F), prefix=p + "mlp."),
+                extras={"post_mixer_norm": norm(p + "n3."), "post_ffn_norm": norm(p + "n4.")} if i == 0 else {}))
+        return ModelSpec(hidden_size=E, vocab_size=V, max_positions=256,
+                         embedding=PartSpec("embedding", dict(vocab_size=V, width=E), prefix="emb."),
+                         layers=layers, schedule=[ScheduleEntry(0), ScheduleEntry(1)], final_norm=norm("final."),
+                         lm_head=PartSpec("lm_head", dict(vocab_size=V, width=E), prefix="head."))
+
+    ARCHITECTURES.register("ToySandwichLM", Architecture("ToySandwichLM", lambda d: dict(d), describe), replace=True)
+
+
+def plain_toy_sandwich(c, W, ids):
+    W = {k: v.double() for k, v in W.items()}
+    T = len(ids)
+    x = W["emb.weight"][torch.tensor(ids)]
+    inv = plain_inv_freq(D, c["theta"], None)
+    pos = torch.arange(T)
+
+    def attn(h, p):
+        q = plain_rope((h @ W[p + "attn.q_proj.weight"].t()).reshape(T, H, D), pos, inv, "interleaved")
+        k = plain_rope((h @ W[p + "attn.k_proj.weight"].t()).reshape(T, K, D), pos, inv, "interleaved")
+        v = (h @ W[p + "attn.v_proj.weight"].t()).reshape(T, K, D)
+        return plain_attention(q, k, v, D ** -0.5) @ W[p + "attn.o_proj.weight"].t()
+
+    def mlp(h, p):
+        return plain_swiglu(h @ W[p + "mlp.gate_proj.weight"].t(), h @ W[p + "mlp.up_proj.weight"].t()) @ W[p + "mlp.down_proj.weight"].t()
+    n = lambda v, name: plain_rmsnorm(v, W[name], c["eps"])
+    x = x + n(attn(n(x, "l0.n1.weight"), "l0."), "l0.n3.weight")
+    x = x + n(mlp(n(x, "l0.n2.weight"), "l0."), "l0.n4.weight")
+    x = x + attn(n(x, "l1.n1.weight"), "l1.")
+    x = x + mlp(n(x, "l1.n2.weight"), "l1.")
+    return n(x, "final.weight") @ W["head.weight"].t()
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 8e-2)])
+def test_a_block_arrangement_with_parts_of_its_own(tmp_path, dtype, tol):
+    """A layer arranged differently (norms after the mixer and after the feed-forward, taken from
+    `LayerSpec.extras`, with workspace the arrangement asks for itself) next to an ordinary layer; in
+    bfloat16 the products leave K-split partial sums that only the built-in arrangement knows of: the model
+    completes the residual stream before it hands it to the foreign one."""
+    register_toy_sandwich()
+    from mdma_b200.engine import Engine, StepEntry
+    from mdma_b200.weights import write_random_model
+    from mdma_b200.weights.safetensors_io import SafetensorsFile
+    cfg = dict(architectures=["ToySandwichLM"], eps=1e-5, theta=10000.0)
+    d = write_random_model(str(tmp_path / "toy3"), cfg, 4, torch.bfloat16 if dtype == "bfloat16" else torch.float32, std=0.08)
+    sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    W = {n: sf.tensor(n).clone().float() for n in sf.entries}
+    assert "l0.n3.weight" in W and "l1.n3.weight" not in W          # the loader learnt the extra tensors from the parts
+    eng = Engine(d, dtype=dtype, max_batch=2, max_context=128, logit_rows=128)
+    g = torch.Generator().manual_seed(2)
+    seqs = [torch.randint(0, V, (n,), generator=g).tolist() for n in (70, 9)]
+    ref = [plain_toy_sandwich(cfg, W, s).numpy() for s in seqs]
+    slots = [eng.acquire() for _ in seqs]
+    cut = [50, 3]
+    out = eng.step([StepEntry(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, seqs, cut)]).cpu().numpy()
+    off = 0
+    for r, c in zip(ref, cut):
+        assert np.abs(out[off:off + c] - r[:c]).max() < tol
+        off += c
+    for step in range(6):
+        out = eng.step([StepEntry(sl, [s[c + step]], [0]) for sl, s, c in zip(slots, seqs, cut)]).cpu().numpy()
+        for row, (r, c) in enumerate(zip(ref, cut)):
+            assert np.abs(out[row] - r[c + step]).max() < tol
+    eng.check_status()
