@@ -363,3 +363,23 @@ def test_an_engine_from_a_seed_holds_the_bits_of_the_folder_written_from_it():
         la = from_seed.step([StepEntry(from_seed.acquire(), ids, [19])]).clone()
         lb = from_folder.step([StepEntry(from_folder.acquire(), ids, [19])])
         assert torch.equal(la, lb)
+
+
+def test_graphs_survive_a_step_that_uses_the_large_scratch():
+    """The kernels' scratch is taken once, for the largest step the engine can run, and never replaced:
+    decode graphs captured after short prompts still hold valid addresses after a 300-token prompt has
+    gone through the block-pair product (which keeps partial tiles in that scratch), in the same engine
+    and in a second engine of the same process."""
+    from mdma_b200.engine import Engine
+    d, c, tensors = make_model(TINY_D, 3, torch.bfloat16, std_scale=SHARP)
+    eng = Engine(d, dtype="bfloat16", max_batch=2, max_context=512)
+    short = prompts_for(TINY_D, (5, 9), 21)
+    long = prompts_for(TINY_D, (300, 140), 22)
+    first = [o.tokens for o in eng.generate(short, max_tokens=16)]
+    scratch = eng.rt.tc.scratch.data_ptr()
+    eng.generate(long, max_tokens=4)
+    other = Engine(d, dtype="bfloat16", max_batch=2, max_context=512)
+    other.generate(long, max_tokens=4)
+    assert eng.rt.tc.scratch.data_ptr() == scratch and other.rt.tc.scratch.data_ptr() != scratch
+    assert [o.tokens for o in eng.generate(short, max_tokens=16)] == first          # replayed graphs
+    assert [o.tokens for o in eng.generate(short, max_tokens=16, use_graphs=False)] == first
