@@ -34,7 +34,14 @@ def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current CUDA stream of the current device, as the launches take it (the stream object
+    of torch costs several microseconds to make, and a step makes hundreds of launches)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch._C._cuda_getDevice()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -50,7 +57,7 @@ LAUNCHES = 0      # kernel launches made through this module (a claim bench.py r
 def _call(libname: str, fn: str, *args, launches: int = 1):
     global LAUNCHES
     LAUNCHES += launches
-    lib = _build.load(libname)
+    lib = _build._loaded.get(libname) or _build.load(libname)
     rc = getattr(lib, fn)(*args)
     if rc != 0:
         raise KernelError(lib.mdma_last_error().decode(errors="replace"))

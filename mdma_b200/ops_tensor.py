@@ -16,6 +16,8 @@ from .ops import KernelError, _call, _f, _i, _need_cuda, _ptr, _stream
 # MDMA_EVEN_SPLIT=0: the block-pair GEMM gives every pair whole tiles only (for comparisons).
 EVEN_SPLIT = os.environ.get("MDMA_EVEN_SPLIT", "1") != "0"
 
+FORCED_ATTENTION = os.environ.get("MDMA_ATTN")        # "tc" or "mma": one attention kernel for every step (comparisons)
+
 PAIR_TOKENS = 128        # steps of more tokens than this run on the block-pair kernel
 
 
@@ -103,7 +105,22 @@ def gemm_supported(n_features: int, k: int) -> bool:
     return k % 8 == 0 and k >= 8
 
 
+_plans: dict = {}
+
+
 def gemm_plan(mode: int, n_tokens: int, n_features: int, k: int, sms: int) -> tuple[int, int]:
+    """(token tile, K splits) the library chooses for a product of these sizes (kept: a step asks
+    for the same few products hundreds of times)."""
+    key = (mode, n_tokens, n_features, k, sms)
+    plan = _plans.get(key)
+    if plan is None:
+        if len(_plans) > 4096:
+            _plans.clear()
+        plan = _plans[key] = _gemm_plan(*key)
+    return plan
+
+
+def _gemm_plan(mode: int, n_tokens: int, n_features: int, k: int, sms: int) -> tuple[int, int]:
     lib = _build.load("tensor")
     bn, splits = ctypes.c_int(0), ctypes.c_int(0)
     lib.mdma_gemm_tc_plan(_i(mode), _i(n_tokens), _i(n_features), _i(k), _i(sms),
@@ -224,8 +241,8 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
     decode kernel, what is between (or outside the tcgen05 kernel's limits) on the mma.sync kernel;
     `impl` ("tc" or "mma") forces one."""
     group = n_heads // n_kv_heads
-    if impl is None and os.environ.get("MDMA_ATTN"):
-        impl = os.environ["MDMA_ATTN"]
+    if impl is None and FORCED_ATTENTION:
+        impl = FORCED_ATTENTION
     if impl is None:
         impl = "tc" if (ctx.max_new * group > 64 and splits is None
                         and attention_tc_supported(n_heads, n_kv_heads, head_dim, view.page_size)) else "mma"

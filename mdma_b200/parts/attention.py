@@ -23,6 +23,9 @@ from .base import Part
 from .linear import Linear
 
 
+FUSED_ROTARY = os.environ.get("MDMA_FUSED_ROTARY", "1") != "0"
+
+
 @MIXERS.register("attention")
 class Attention(Part):
     graph_safe = True      # forward reads no host-side per-step values
@@ -130,7 +133,7 @@ class Attention(Part):
         the 8B layer shape: the chain of a layer takes 93.6 us against 96.4 us at batch 8, but 139 us
         against 135 us at batch 64, where each of many small blocks repeats the work on the projection
         row).  MDMA_FUSED_ROTARY=0 turns it off, for comparisons."""
-        if self.rt.attention != "fast" or not hasattr(self.position, "rotary_table") or os.environ.get("MDMA_FUSED_ROTARY") == "0":
+        if self.rt.attention != "fast" or not hasattr(self.position, "rotary_table") or not FUSED_ROTARY:
             return False
         from .. import ops_tensor
         sms = self.rt.tc.sms if self.rt.tc is not None else 0
