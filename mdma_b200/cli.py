@@ -5,6 +5,8 @@ a PROMPT is a list of token ids ("5,17,3" or "5 17 3"); several prompts form a
 batch.  Options the reference has keep its names and meanings (--max-tokens,
 --vram-bytes, --reserve-mib, --json; MDMA_JSON for mdma-run); --backend and
 --gpu-layers do not exist because there is one backend and one device.
+`mdma replay ...` is the trace replay program (bin/trace_run); the benchmark is
+`bench.py` at the top of the repository.
 """
 from __future__ import annotations
 
@@ -41,8 +43,14 @@ def cmd_run(args) -> int:
         print("--max-tokens must be positive", file=sys.stderr)
         return 2
     need_ctx = max(len(p) for p in prompts) + args.max_tokens
+    source = {"model_dir": args.model}
+    if args.random_weights is not None:
+        # no weights are read: the configuration (a config.json, or a folder that holds one) and a seed
+        path = os.path.join(args.model, "config.json") if os.path.isdir(args.model) else args.model
+        with open(path, "r", encoding="utf-8") as f:
+            source = {"config": json.load(f), "seed": args.random_weights}
     try:
-        engine = Engine(args.model, dtype=args.dtype, max_batch=min(args.max_batch, len(prompts)),
+        engine = Engine(**source, dtype=args.dtype, max_batch=min(args.max_batch, len(prompts)),
                         max_context=args.max_context or None, reserve_mib=args.reserve_mib,
                         vram_bytes=args.vram_bytes, context_hint=need_ctx,
                         history_cap=max(64, args.repetition_window))
@@ -109,6 +117,8 @@ def build_parser() -> argparse.ArgumentParser:
     run.add_argument("--repetition-window", type=int, default=64)
     run.add_argument("--seed", type=int, default=0)
     run.add_argument("--stop-ids", default=None, help="token ids that end a sequence (default: the config's eos)")
+    run.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                     help="seeded random weights instead of the folder's (MODEL may then be a config.json)")
     _add_engine_args(run)
     run.set_defaults(fn=cmd_run)
 
@@ -123,6 +133,8 @@ def build_parser() -> argparse.ArgumentParser:
     plan.add_argument("--json", action="store_true")
     plan.set_defaults(fn=cmd_plan)
 
+    sub.add_parser("replay", help="feed given token ids step by step and write logits (= bin/trace_run)", add_help=False)
+
     init = sub.add_parser("init-random", help="write a model folder with seeded random weights")
     init.add_argument("config", help="a config.json")
     init.add_argument("out")
@@ -133,6 +145,10 @@ def build_parser() -> argparse.ArgumentParser:
 
 
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "replay":            # its own options, taken as they are
+        from .replay import main as replay_main
+        return replay_main(argv[1:])
     args = build_parser().parse_args(argv)
     try:
         return args.fn(args)

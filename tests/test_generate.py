@@ -113,6 +113,12 @@ def test_command_line(tmp_path):
     assert json.loads(res.stdout.strip().splitlines()[-1])["tokens"][:5] == json.loads(
         subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mdma"), "run", d, ",".join(map(str, p)),
                         "--max-tokens", "5", "--json"], capture_output=True, text=True, env=env).stdout.strip().splitlines()[-1])["tokens"]
+    # seeded random weights from the configuration alone: the same tokens as from the folder written with that seed
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mdma"), "run", os.path.join(d, "config.json"),
+                          ",".join(map(str, p)), "--max-tokens", "5", "--dtype", "float32", "--json", "--random-weights", "0"],
+                         capture_output=True, text=True, env=env)
+    assert res.returncode == 0, res.stderr
+    assert json.loads(res.stdout.strip().splitlines()[-1])["tokens"] == want
     res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mdma"), "plan", d, "--ctx", "64", "--json"],
                          capture_output=True, text=True, env=env)
     plan = json.loads(res.stdout)
