@@ -299,7 +299,8 @@ class StepMeta:
 
 
 @pytest.mark.parametrize("H,K,hd,window", [(8, 2, 128, 0), (6, 2, 48, 0), (4, 4, 16, 0), (12, 2, 64, 0),
-                                           (6, 1, 80, 0), (8, 2, 128, 100), (5, 5, 112, 33), (32, 8, 128, 0)])
+                                           (6, 1, 80, 0), (8, 2, 128, 100), (5, 5, 112, 33), (32, 8, 128, 0),
+                                           (40, 2, 64, 0), (64, 1, 32, 0)])      # groups of 20 and 64 query heads
 @pytest.mark.parametrize("case", ["prefill", "chunked", "decode", "decode_split", "decode_long", "decode_many1",
                                   "decode_many3", "decode_many4", "decode_page16", "prefill_tc", "chunked_tc"])
 @pytest.mark.parametrize("poison", [False, True])

@@ -11,7 +11,7 @@ import torch
 
 from plain_llama import plain_forward
 from replay_util import assert_close, replay
-from tiny import SHARP, TINY_A, TINY_B, TINY_C, TINY_D, make_model
+from tiny import SHARP, TINY_A, TINY_B, TINY_C, TINY_D, TINY_E, make_model
 
 pytestmark = pytest.mark.gpu
 
@@ -251,3 +251,22 @@ def test_padding_and_batch_mates_change_nothing():
                                                    for rid, ids in reqs.items()], "end": list(reqs)}],
                       max_tokens=256, vocab=V)[0]
     assert np.abs(alone[0] - together[0]).max() < 2e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_heads_wider_than_the_fast_attention_takes(dtype):
+    """head_dim 160 (a multiple of 16 beyond the tensor-core attention's 128): the engine takes the plain
+    attention kernel for it, in bfloat16 too; whole prompts, then tokens one by one, two unequal requests."""
+    d, c, tensors = make_model(TINY_E, 6, torch.bfloat16, std_scale=SHARP)
+    V = TINY_E["vocab_size"]
+    reqs = requests_for(TINY_E, 60, [90, 41])
+    ref = {rid: oracle(c, tensors, ids, dtype) for rid, ids in reqs.items()}
+    head = {"r0": 70, "r1": 21}
+    steps = [{"entries": [{"id": rid, "tokens": reqs[rid][:head[rid]], "want": list(range(head[rid]))} for rid in reqs], "end": []}]
+    index = [[(rid, p) for rid in reqs for p in range(head[rid])]]
+    for j in range(20):
+        steps.append({"entries": [{"id": rid, "tokens": [reqs[rid][head[rid] + j]], "want": [0]} for rid in reqs],
+                      "end": list(reqs) if j == 19 else []})
+        index.append([(rid, head[rid] + j) for rid in reqs])
+    got = replay(d, dtype, steps, max_tokens=256, vocab=V, extra_args=("--poison-unused",))
+    check_rows(got, index, ref, dtype, "wide heads")

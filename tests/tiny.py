@@ -47,6 +47,14 @@ TINY_D = dict(
     rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=2304)
 
 
+# heads wider than the tensor-core attention kernels take (128): the plain attention kernel serves them
+TINY_E = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama",
+    num_hidden_layers=2, hidden_size=104, num_attention_heads=2, num_key_value_heads=1, head_dim=160,
+    intermediate_size=136, vocab_size=211, rope_theta=10000.0, rope_scaling=None, rms_norm_eps=1e-5,
+    tie_word_embeddings=True, max_position_embeddings=192)
+
+
 def make_model(cfg: dict, seed: int, dtype=torch.float32, root=None, std_scale: float = 1.0):
     """Write a model folder into a fresh temporary directory; returns (dir, config dict, tensors).
     Matrices are N(0, 0.02 * std_scale)."""
