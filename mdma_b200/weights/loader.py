@@ -101,12 +101,47 @@ def resident_dtype(spec: TensorSpec, stored: torch.dtype, compute: torch.dtype) 
     return torch.float32 if stored in (torch.float32, torch.float16) else torch.bfloat16
 
 
+class _Staging:
+    """Two pinned host buffers that take turns: a piece of a tensor is converted into one (on the host,
+    to the dtype it is kept in) while the copy of the piece before runs out of the other.  The reference
+    stages its uploads through one host buffer the size of the largest tensor (src/model/planning.rs:44-53);
+    here the pieces are of a fixed size, so host memory does not grow with the model."""
+
+    def __init__(self, nbytes: int):
+        self.nbytes = max(int(nbytes), 1 << 12)
+        self.bufs = [torch.empty(self.nbytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.events = [torch.cuda.Event(), torch.cuda.Event()]
+        self.turn = 0
+
+    def copy(self, src: torch.Tensor, dst: torch.Tensor) -> None:
+        """dst (device, contiguous) <- src (host, same shape, any float/int dtype)."""
+        flat_src, flat_dst = src.reshape(-1), dst.view(-1) if dst.is_contiguous() else None
+        if flat_dst is None:
+            dst.copy_(src.to(dst.dtype))
+            return
+        per = self.nbytes // dst.element_size()
+        for lo in range(0, flat_dst.numel(), per):
+            hi = min(flat_dst.numel(), lo + per)
+            self.turn ^= 1
+            self.events[self.turn].synchronize()            # the copy that used this buffer last is done
+            stage = self.bufs[self.turn][:(hi - lo) * dst.element_size()].view(dst.dtype)
+            stage.copy_(flat_src[lo:hi])                    # dtype conversion on the host, into pinned memory
+            flat_dst[lo:hi].copy_(stage, non_blocking=True)
+            self.events[self.turn].record()
+
+    def finish(self) -> None:
+        for e in self.events:
+            e.synchronize()
+
+
 def load_tensors(model_dir: str, expected: dict[str, TensorSpec], compute: torch.dtype,
-                 device: Optional[torch.device] = None, into: Optional[dict] = None) -> dict[str, torch.Tensor]:
+                 device: Optional[torch.device] = None, into: Optional[dict] = None,
+                 staging_bytes: int = 64 << 20) -> dict[str, torch.Tensor]:
     """Validate the folder against `expected`, then fetch each tensor by name.  With `into`
     (name -> a tensor of the right shape and resident dtype, e.g. a view of an engine's arena)
-    the values are copied there and no memory is taken for them here: the dtype is converted on
-    the host and the bytes go from the mapped file to their place."""
+    the values are copied there and no device memory is taken for them here: pieces of
+    `staging_bytes` are converted on the host into pinned memory and copied from there while the
+    next piece is being converted."""
     files = open_model_files(model_dir)
     entries = {}
     for sf in files:
@@ -114,6 +149,7 @@ def load_tensors(model_dir: str, expected: dict[str, TensorSpec], compute: torch
     check_entries(entries, expected, where=model_dir)
     by_file = {sf.path: sf for sf in files}
     out: dict[str, torch.Tensor] = {}
+    staging = None
     for name, spec in expected.items():
         e = entries[name]
         t = by_file[e.file].tensor(name)
@@ -123,12 +159,19 @@ def load_tensors(model_dir: str, expected: dict[str, TensorSpec], compute: torch
             if dst.dtype != dtype or tuple(dst.shape) != tuple(spec.shape):
                 raise ValueError(f"{name}: the place prepared for it is {list(dst.shape)} {dst.dtype}, "
                                  f"it is {list(spec.shape)} {dtype}")
-            dst.copy_(t.to(dtype=dtype))
+            if dst.is_cuda:
+                if staging is None:
+                    staging = _Staging(staging_bytes)
+                staging.copy(t, dst)
+            else:
+                dst.copy_(t.to(dtype=dtype))
             out[name] = dst
         elif device is not None:
             out[name] = t.to(device=device, dtype=dtype, non_blocking=False).contiguous()
         else:
             out[name] = t.to(dtype=dtype).contiguous()
+    if staging is not None:
+        staging.finish()
     return out
 
 

@@ -389,3 +389,19 @@ def test_graphs_survive_a_step_that_uses_the_large_scratch():
     assert eng.rt.tc.scratch.data_ptr() == scratch and other.rt.tc.scratch.data_ptr() != scratch
     assert [o.tokens for o in eng.generate(short, max_tokens=16)] == first          # replayed graphs
     assert [o.tokens for o in eng.generate(short, max_tokens=16, use_graphs=False)] == first
+
+
+def test_loading_in_pieces_through_pinned_memory():
+    """Tensors larger than the staging pieces (here 4 KiB) arrive whole, whatever their stored dtype."""
+    from mdma_b200.config import load_config
+    from mdma_b200.engine.model import DecoderModel
+    from mdma_b200.weights import load_tensors, resident_dtype
+    d, c, tensors = make_model(TINY_C, 2, torch.float32)
+    arch, cfg = load_config(d)
+    expected = DecoderModel(arch.describe(cfg)).expected_tensors()
+    for compute in (torch.bfloat16, torch.float32):
+        into = {n: torch.full(ts.shape, 7.0, dtype=resident_dtype(ts, torch.float32, compute), device="cuda:0")
+                for n, ts in expected.items()}
+        load_tensors(d, expected, compute, torch.device("cuda:0"), into=into, staging_bytes=4096)
+        for n, t in tensors.items():
+            assert torch.equal(into[n].cpu(), t.to(into[n].dtype)), n
