@@ -91,17 +91,6 @@ class DecodeSession:
         self.seq_slot[:B].copy_(self._host[2 * cap:2 * cap + B], non_blocking=True)
         self.engine.h2d_bytes += 16 * B
 
-    def feed(self, tokens: Sequence[int]) -> None:
-        """The same sequences go on: only this step's input tokens go up (from pinned memory,
-        asynchronously; positions and slots are already on the device).  The caller has read the
-        previous step's tokens, so the staging buffer is free."""
-        B = len(self.slots)
-        if len(tokens) != B:
-            raise StepError(f"{len(tokens)} tokens for {B} live sequences")
-        self._host_np[:B] = tokens
-        self.ids[:B].copy_(self._host[:B], non_blocking=True)
-        self.engine.h2d_bytes += 4 * B
-
     # ---- one step ----------------------------------------------------------
     @property
     def _draws(self) -> bool:
@@ -201,10 +190,6 @@ class DecodeSession:
             self._kept = self.max_run
         return n
 
-    def step_async(self, histories=None, use_graph: bool = True) -> None:
-        """One decode step; tokens stay on the device."""
-        self.run(1, histories, use_graph)
-
     def read(self) -> list[tuple[list[int], list[int]]]:
         """The tokens and non-finite flags of every step since the last read, oldest first
         (one copy for all of them; synchronises).  Raises `KernelError` if a kernel's bounded
@@ -226,7 +211,3 @@ class DecodeSession:
         if self.engine.rt.tc is not None:
             self.engine.raise_on_status(status)
         return out
-
-    def read_tokens(self) -> tuple[list[int], list[int]]:
-        """The tokens (and non-finite flags) the last step selected."""
-        return self.read()[-1]

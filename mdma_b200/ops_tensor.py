@@ -128,11 +128,6 @@ def _gemm_plan(mode: int, n_tokens: int, n_features: int, k: int, sms: int) -> t
     return bn.value, splits.value
 
 
-def reserve_scratch(device: torch.device, floats: int) -> None:
-    """Make the default state's scratch at least this large (call outside graph capture)."""
-    _device_state(device).need(floats, "reserve_scratch")
-
-
 class Pending:
     """Partial sums of a K-split product that still wait in the scratch to be added
     up into (or onto) `target`: [splits, rows, cols] floats."""
