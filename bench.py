@@ -118,10 +118,10 @@ def prefill_flops(cfg, layers, T):
     return 2 * T * body + 2 * head + attn          # the head runs on the last row only
 
 
-def decode_bytes(cfg, layers, batch, context):
+def decode_bytes(cfg, layers, batch, context, elem_bytes=2):
     body, head = matmul_params(cfg, layers)
     kv_row = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * layers
-    return 2 * (body + head) + batch * context * kv_row
+    return (2 * (body + head) + batch * context * kv_row) * elem_bytes // 2
 
 
 def main() -> int:
@@ -141,6 +141,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement (profiling runs)")
     ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill (profiling runs)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="float32: the true 32-bit engine (CUDA-core kernels), for the record; the headline is bfloat16")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -167,7 +169,7 @@ def main() -> int:
     hbm_gbs, bf16_tflops, peak_src, sustained = peaks()
     torch.cuda.set_device(0)
     max_batch = max(args.batch, 1 if args.no_points else 64)
-    eng = Engine(config=cfg, seed=0, dtype="bfloat16", max_batch=max_batch,
+    eng = Engine(config=cfg, seed=0, dtype=args.dtype, max_batch=max_batch,
                  max_context=max(args.context, args.prefill_tokens))
     sampler = eng.sampler
     gen = torch.Generator().manual_seed(0)
@@ -237,7 +239,7 @@ def main() -> int:
     value = args.batch * 1000.0 / ms_step
     ctx_end = int(mean_prompt) + warmup + args.steps
     avg_ctx = mean_prompt + warmup + args.steps / 2
-    bytes_step = decode_bytes(cfg, args.layers, args.batch, avg_ctx)
+    bytes_step = decode_bytes(cfg, args.layers, args.batch, avg_ctx, 2 if args.dtype == "bfloat16" else 4)
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
 
     # end to end: host token lists in, host token lists out, through Generator.generate
@@ -270,7 +272,7 @@ def main() -> int:
             f"prompts of {args.prompt_len_range[0]}-{args.prompt_len_range[1]} tokens)"),
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic (uniform random token ids, random N(0,0.02) weights)",
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic (uniform random token ids, random N(0,0.02) weights)",
         "impl": "ours",
         "config": {"model": shape_name, "layers": args.layers, "layers_full": FULL_LAYERS,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],

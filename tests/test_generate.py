@@ -405,3 +405,34 @@ def test_loading_in_pieces_through_pinned_memory():
         load_tensors(d, expected, compute, torch.device("cuda:0"), into=into, staging_bytes=4096)
         for n, t in tensors.items():
             assert torch.equal(into[n].cpu(), t.to(into[n].dtype)), n
+
+
+def test_the_benchmark_layer_shape_in_bfloat16_against_true_32_bit():
+    """Two layers of the Llama-3.1-8B shape (hidden 4096, 32/8 heads of 128, intermediate 14336, vocabulary
+    128,256; random weights from a seed): prompts of 300, 70 and 9 tokens in one step, then four steps of
+    one token each, through the tensor-core kernels at their real sizes (block-pair products, the SwiGLU
+    product's even split, K splits left for the norms, the head over 128k rows) against the same model in
+    the float32 engine (CUDA-core kernels, no reduced precision anywhere).  The float32 engine keeps the
+    seed's weights unrounded, so the difference includes rounding the weights to bfloat16 once:
+    measured 0.11 at most on logits of deviation 1.28, 1.8 % of a row's deviation in the root mean square."""
+    import numpy as np
+    import bench
+    from mdma_b200.engine import Engine, StepEntry
+    cfg = dict(bench.LLAMA_31_8B, num_hidden_layers=2, max_position_embeddings=1024)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in (300, 70, 9)]
+    res = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(config=cfg, seed=0, dtype=dtype, max_batch=3, max_context=512, logit_rows=16)
+        slots = [eng.acquire() for _ in prompts]
+        out = [eng.step([StepEntry(s, p, [0, len(p) // 2, len(p) - 1]) for s, p in zip(slots, prompts)]).cpu().numpy().copy()]
+        for j in range(4):
+            out.append(eng.step([StepEntry(s, [p[j]], [0]) for s, p in zip(slots, prompts)]).cpu().numpy().copy())
+        eng.check_status()
+        res[dtype] = np.concatenate(out).astype(np.float64)
+        del eng
+    a, b = res["float32"], res["bfloat16"]
+    assert np.isfinite(b).all() and 1.0 < a.std() < 1.6
+    err = np.abs(a - b)
+    assert err.max() < 0.2, err.max()
+    assert (np.sqrt((err ** 2).mean(1)) / a.std(1)).max() < 0.03
