@@ -209,13 +209,27 @@ def attention_splits(n_seqs: int, max_new: int, max_len: int, n_heads: int, n_kv
     group = n_heads // n_kv_heads
     key_blocks = max(1, -(-max_len // 64))
     if max_new == 1 and group <= 16:
-        # decode kernel: a block's warps each take 32-key tiles in turn.  Short contexts: one block of
-        # eight warps per (sequence, kv head), no merge kernel; else four warps and a K split.
+        # decode kernel: a block's warps each take 32-key tiles in turn.  One block of eight warps per
+        # (sequence, kv head) and no merge kernel, unless that leaves most of the device idle:
+        #  - a handful of sequences (blocks x 4 within three quarters of the SMs): four blocks per
+        #    (sequence, kv head), six for long contexts; a round of tiles costs a block about 1.3 us and a
+        #    merge kernel about as much (measured in the layer chain at the 8B shape, context 580: batch 1
+        #    94.1 -> 89.9 us, batch 2 95.0 -> 91.2, batch 3 93.8 -> 92.3, batch 4 no gain);
+        #  - contexts beyond 1,024 with fewer blocks than SMs: as many splits as keep every block resident
+        #    with four warps (three blocks per SM).
+        # The choice is made from the context rounded up to 1,024, as the replayed decode graphs see it, so
+        # that a step run on its own and the same step replayed add up in the same order.
+        max_len = -(-max_len // 1024) * 1024
         blocks = n_seqs * n_kv_heads
-        if max_len <= 1024 or blocks >= sms:
+        if blocks >= sms:
             return 1
+        few = blocks * 4 <= (3 * sms) // 4
+        if max_len <= 1024:
+            return 4 if few else 1
+        if few:
+            return 6
         rounds = -(-max_len // (32 * 4))           # four warps x 32 keys per round
-        return max(2, min(-(-3 * sms // blocks), rounds, 32))
+        return max(2, min(3 * sms // blocks, rounds, 32))
     tile_tokens = max(1, 64 // group)
     blocks = -(-max_new // tile_tokens) * n_seqs * n_kv_heads
     if blocks >= 2 * sms:
