@@ -168,7 +168,7 @@ def main() -> int:
     cfg = dict(shape_cfg, num_hidden_layers=args.layers)
     hbm_gbs, bf16_tflops, peak_src, sustained = peaks()
     torch.cuda.set_device(0)
-    max_batch = max(args.batch, 1 if args.no_points else 64)
+    max_batch = args.batch
     eng = Engine(config=cfg, seed=0, dtype=args.dtype, max_batch=max_batch,
                  max_context=max(args.context, args.prefill_tokens))
     sampler = eng.sampler
@@ -289,12 +289,22 @@ def main() -> int:
     }
 
     if not args.no_points:
+        # the other batch sizes, each on an engine built for that many sequences (as a deployment for that
+        # batch size would be: the kernels plan some choices for the most sequences an engine holds)
+        out["prefill"] = time_prefill()
         points = {}
         for b in (1, 64):
+            if b != eng.max_slots:
+                eng.check_status()
+                sampler = eng = None
+                import gc
+                gc.collect()
+                torch.cuda.empty_cache()
+                eng = Engine(config=cfg, seed=0, dtype=args.dtype, max_batch=b, max_context=max(args.context, args.prefill_tokens))
+                sampler = eng.sampler
             ms_b, _, _ = time_decode(b, max(8, args.steps // 2))
             points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 2)
         out["points"] = points
-        out["prefill"] = time_prefill()
     out["clocks"] = clock.stop()
     eng.check_status()
     print(json.dumps(out))

@@ -50,6 +50,7 @@ class DecodeSession:
         self._host_np = self._host.numpy()            # the same pinned words, written without a tensor in between
         self._ring_host = torch.empty(tuple(self.ring.shape), dtype=torch.int32).pin_memory()
         self.ctx = StepContext(engine.rt, engine.workspace)
+        self.ctx.most_seqs = engine.max_slots
         self.steps_done: list[int] = []
         self.launches_per_step = 0          # kernels in one step (counted at the eager first run)
         self._state_stale = True

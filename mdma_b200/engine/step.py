@@ -60,6 +60,7 @@ class StepContext:
         self._workspace = workspace
         self.n_tokens = self.n_seqs = self.n_want = 0
         self.max_new = self.max_len = 0
+        self.most_seqs = None               # the most sequences the engine holds (kernels may plan for it)
         self.ids = self.tok_seq = self.tok_pos = self.seq_slot = self.seq_start = self.seq_pos0 = None
         self.want_rows = None
 
@@ -277,6 +278,7 @@ class Engine:
             self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
             self._status_event = None
         self.ctx = StepContext(self.rt, self.workspace)
+        self.ctx.most_seqs = self.max_slots
         self.forward_passes = 0
         self.h2d_bytes = self.d2h_bytes = 0     # bytes of step inputs copied up / results copied down so far
         self._session = None

@@ -204,14 +204,17 @@ def attention_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
             and n_heads // n_kv_heads <= 64)
 
 
-def attention_splits(n_seqs: int, max_new: int, max_len: int, n_heads: int, n_kv_heads: int, sms: int) -> int:
-    """How many ways to divide a tile's keys so that the grid fills the device."""
+def attention_splits(n_seqs: int, max_new: int, max_len: int, n_heads: int, n_kv_heads: int, sms: int,
+                     most_seqs: Optional[int] = None) -> int:
+    """How many ways to divide a tile's keys so that the grid fills the device.  `most_seqs`: the most
+    sequences the engine can hold; the choice for a handful of sequences is made from it, not from the
+    live batch, so that a request's arithmetic does not change when a batch mate ends."""
     group = n_heads // n_kv_heads
     key_blocks = max(1, -(-max_len // 64))
     if max_new == 1 and group <= 16:
         # decode kernel: a block's warps each take 32-key tiles in turn.  One block of eight warps per
         # (sequence, kv head) and no merge kernel, unless that leaves most of the device idle:
-        #  - a handful of sequences (blocks x 4 within three quarters of the SMs): four blocks per
+        #  - an engine for a handful of sequences (their blocks x 4 within three quarters of the SMs): four blocks per
         #    (sequence, kv head), six for long contexts; a round of tiles costs a block about 1.3 us and a
         #    merge kernel about as much (measured in the layer chain at the 8B shape, context 580: batch 1
         #    94.1 -> 89.9 us, batch 2 95.0 -> 91.2, batch 3 93.8 -> 92.3, batch 4 no gain);
@@ -223,7 +226,7 @@ def attention_splits(n_seqs: int, max_new: int, max_len: int, n_heads: int, n_kv
         blocks = n_seqs * n_kv_heads
         if blocks >= sms:
             return 1
-        few = blocks * 4 <= (3 * sms) // 4
+        few = (most_seqs or n_seqs) * n_kv_heads * 4 <= (3 * sms) // 4
         if max_len <= 1024:
             return 4 if few else 1
         if few:
@@ -276,7 +279,8 @@ def attention(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_heads: int, n_k
     st = st or _device_state(qkv.device)
     flush_pending(qkv.device, st)
     if splits is None:
-        splits = attention_splits(ctx.n_seqs, ctx.max_new, ctx.max_len, n_heads, n_kv_heads, st.sms)
+        splits = attention_splits(ctx.n_seqs, ctx.max_new, ctx.max_len, n_heads, n_kv_heads, st.sms,
+                                  getattr(ctx, "most_seqs", None))
     st.need(ctx.n_tokens * n_heads * splits * (head_dim + 2) if splits > 1 else 0, "attention over split keys")
     _call("tensor", "mdma_attention_mma_paged", _ptr(qkv), _i(qkv.stride(0)), _ptr(view.k), _ptr(view.v),
           _i(view.k.shape[0] if view.k.is_contiguous() and view.v.is_contiguous() else 0), _ptr(ctx.seq_start), _ptr(ctx.seq_pos0), _ptr(ctx.seq_slot), _ptr(view.page_table),
@@ -314,7 +318,7 @@ def attention_decode_rotary(ctx, qkv: torch.Tensor, view, out: torch.Tensor, n_h
     else:
         flush_pending(qkv.device, st)
     if splits is None:
-        splits = attention_splits(ctx.n_seqs, 1, ctx.max_len, n_heads, n_kv_heads, st.sms)
+        splits = attention_splits(ctx.n_seqs, 1, ctx.max_len, n_heads, n_kv_heads, st.sms, getattr(ctx, "most_seqs", None))
     # the attention's own partials (keys split over blocks) lie behind the projection's
     used = -(-proj_splits * stride // 64) * 64
     need = ctx.n_tokens * n_heads * splits * (head_dim + 2) if splits > 1 else 0

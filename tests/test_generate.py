@@ -436,3 +436,38 @@ def test_the_benchmark_layer_shape_in_bfloat16_against_true_32_bit():
     err = np.abs(a - b)
     assert err.max() < 0.2, err.max()
     assert (np.sqrt((err ** 2).mean(1)) / a.std(1)).max() < 0.03
+
+
+def test_random_traffic_replayed_runs_equal_the_step_by_step_loop():
+    """Random batches (1-9 prompts of 1 to context-5 tokens, budgets of 1-40 tokens, greedy or sampled with
+    random options, random stop tokens, runs of 1, 3 or 8 replayed steps): the same tokens and finish
+    reasons as the loop that runs every step on its own, sequences ending inside runs and batches shrinking
+    included, and no slot or page lost.  The kernels' choices depend on the engine's capacity, not on the
+    live batch, within these sizes; that is what makes the two loops agree bit for bit."""
+    import random
+    from mdma_b200.engine import Engine
+    from mdma_b200.engine.generate import Generator
+    from mdma_b200.sampling import SamplingParams
+    rnd = random.Random(0)
+    for cfg, seed, wd, dtype in ((TINY_D, 3, torch.bfloat16, "bfloat16"), (TINY_B, 1, torch.bfloat16, "bfloat16"),
+                                 (TINY_C, 2, torch.float32, "float32")):
+        d, c, tensors = make_model(cfg, seed, wd, std_scale=SHARP)
+        ctx = min(cfg["max_position_embeddings"], 700)
+        eng = Engine(d, dtype=dtype, max_batch=6, max_context=ctx, max_tokens=6 * 64 * 4)
+        g = torch.Generator().manual_seed(seed)
+        for it in range(40):
+            lens = [max(1, min(rnd.choice([1, 2, 5, 17, 63, 64, 65, 100, 130, ctx - 40, ctx - 5]), ctx - 1))
+                    for _ in range(rnd.randint(1, 9))]
+            prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+            max_tokens = rnd.choice([1, 2, 7, 8, 9, 20, 40])
+            params = SamplingParams.greedy() if rnd.random() < 0.5 else SamplingParams(
+                rnd.choice([0.5, 0.8, 1.2]), rnd.choice([1.0, 0.9]), rnd.choice([0.0, 0.05]), rnd.choice([1.0, 1.3]),
+                rnd.choice([0, 16, 64, 200]), rnd.randint(0, 99))
+            stop = [rnd.randrange(cfg["vocab_size"]) for _ in range(rnd.choice([0, 0, 3, 10]))]
+            runs = Generator(eng, run_ahead=rnd.choice([1, 3, 8])).generate(prompts, max_tokens, params, stop)
+            steps = Generator(eng, use_graphs=False).generate(prompts, max_tokens, params, stop)
+            assert [(o.tokens, o.finish_reason) for o in runs] == [(o.tokens, o.finish_reason) for o in steps], (it, lens)
+            eng.cache.check()
+            assert not eng.cache.lengths
+        eng.check_status()
+        del eng
