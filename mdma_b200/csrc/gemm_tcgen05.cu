@@ -770,7 +770,21 @@ int mdma_gemm_tc_supported(int n_features, int K) { return (K % 8 == 0 && K >= 8
 // `splits` <= 0 asks the library to choose.
 // `splits_out` < 0 means: split K that many ways inside a cluster (no scratch, reduced in shared memory).
 int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_count, int* bn_out, int* splits_out) {
-    if (n_tokens > 128) {      // many tokens: block pairs, 256 features x 256 tokens per pair (`bn` code 512)
+    if (n_tokens > 128) {
+        // Many tokens: block pairs, 256 features x 256 tokens per pair (`bn` code 512).  But with few
+        // feature tiles and 129-512 tokens the pairs leave most of the device idle (the down product of 256
+        // tokens: 16 pairs for 74 SM pairs, 87.6 us; O: 32.2 us): the one-block kernel with token tiles of 128
+        // and a K split that gives every SM a block takes 50.1 us and 24.8 us there (512 tokens: 79.9 against
+        // 89.1 us and 29.5 against 32.9 us).  Two weight matrices (SwiGLU) stay with the pairs (61 against 95 us).
+        const long pair_tiles = (long)((n_features + 255) / 256) * ((n_tokens + 255) / 256);
+        if (mode != kTcSwiGLU && n_tokens <= 512 && pair_tiles * 10 < (long)(sm_count / 2) * 6) {
+            const int k_blocks = (K + kBK - 1) / kBK;
+            const long tiles = (long)((n_features + kBM - 1) / kBM) * ((n_tokens + 127) / 128);
+            int splits = (int)(sm_count / tiles);
+            if (splits > k_blocks / 4) splits = k_blocks / 4;
+            if (splits < 1) splits = 1;
+            *bn_out = 128; *splits_out = splits; return 0;
+        }
         *bn_out = 512; *splits_out = 1; return 0;
     }
     int bn = 16;
