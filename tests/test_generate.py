@@ -407,9 +407,12 @@ def test_loading_in_pieces_through_pinned_memory():
             assert torch.equal(into[n].cpu(), t.to(into[n].dtype)), n
 
 
-def test_the_benchmark_layer_shape_in_bfloat16_against_true_32_bit():
+@pytest.mark.parametrize("lengths", [(300, 70, 9), (150, 70, 9)])
+def test_the_benchmark_layer_shape_in_bfloat16_against_true_32_bit(lengths):
     """Two layers of the Llama-3.1-8B shape (hidden 4096, 32/8 heads of 128, intermediate 14336, vocabulary
-    128,256; random weights from a seed): prompts of 300, 70 and 9 tokens in one step, then four steps of
+    128,256; random weights from a seed): prompts of 300, 70 and 9 tokens in one step (or 150, 70 and 9: a
+    step of 129-256 tokens, whose O and down products run one block per tile with a K split left for the
+    norms), then four steps of
     one token each, through the tensor-core kernels at their real sizes (block-pair products, the SwiGLU
     product's even split, K splits left for the norms, the head over 128k rows) against the same model in
     the float32 engine (CUDA-core kernels, no reduced precision anywhere).  The float32 engine keeps the
@@ -420,7 +423,7 @@ def test_the_benchmark_layer_shape_in_bfloat16_against_true_32_bit():
     from mdma_b200.engine import Engine, StepEntry
     cfg = dict(bench.LLAMA_31_8B, num_hidden_layers=2, max_position_embeddings=1024)
     g = torch.Generator().manual_seed(0)
-    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in (300, 70, 9)]
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lengths]
     res = {}
     for dtype in ("float32", "bfloat16"):
         eng = Engine(config=cfg, seed=0, dtype=dtype, max_batch=3, max_context=512, logit_rows=16)

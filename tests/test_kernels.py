@@ -489,7 +489,9 @@ def test_gemm_simt_rows_do_not_depend_on_their_neighbours():
 
 @pytest.mark.parametrize("M,N,K,mode", [(1, 128, 64, 0), (9, 200, 72, 0), (130, 1000, 1032, 0), (600, 264, 256, 0),
                                         (7, 520, 2048, 1), (300, 136, 512, 1), (3, 300, 264, 2), (257, 384, 640, 2),
-                                        (2, 331, 8, 0)])
+                                        (2, 331, 8, 0),
+                                        # 129-512 tokens and few feature tiles: one block per tile, K split by the plan
+                                        (200, 520, 4096, 0), (300, 136, 2048, 1), (512, 264, 1024, 1), (129, 128, 8192, 0)])
 def test_gemm_tensor(M, N, K, mode):
     from mdma_b200 import ops_tensor
     ops = ops_mod()
