@@ -26,6 +26,30 @@ static inline int fail(const char* fmt, ...) {
     va_end(ap);
     return 1;
 }
+// What a matrix product adds on its way out: a vector over the output features (for the second matrix of
+// a gated product too), kept as float32 or bfloat16, and which activation a gated product applies to its gate.
+enum Activation : int { kActSilu = 0, kActGeluTanh = 1 };
+struct Ending {
+    const void* bias;     // [n_features] or null
+    const void* bias2;    // the second matrix's, or null
+    int bias_dtype;       // DType of both
+    int act;              // Activation, gated products only
+};
+__device__ __forceinline__ float ending_bias(const void* b, int dtype, int f) {
+    if (b == nullptr) return 0.f;
+    return dtype == kF32 ? reinterpret_cast<const float*>(b)[f] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[f]);
+}
+// act(g) of a gated feed-forward in plain float arithmetic (the 32-bit engine) ...
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    if (act == kActGeluTanh) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + expf(-g));
+}
+// ... and with the fast exponential (the bfloat16 engine): 0.5 (1 + tanh t) = 1 / (1 + e^(-2t)).
+__device__ __forceinline__ float gate_activation_fast(float g, int act) {
+    if (act == kActGeluTanh) return g / (1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + __expf(-g));
+}
+
 #define MDMA_REQUIRE(cond, ...) \
     do { if (!(cond)) return ::mdma::fail(__VA_ARGS__); } while (0)
 #define MDMA_LAUNCH_OK(name) \

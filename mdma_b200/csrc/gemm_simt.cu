@@ -12,7 +12,7 @@ namespace mdma {
 enum GemmMode : int {
     kStore = 0,        // out = acc
     kAccumulate = 1,   // out += acc        (the residual stream, float)
-    kSwiGLU = 2,       // out = silu(acc_gate) * acc_up, with a second weight
+    kSwiGLU = 2,       // out = act(acc_gate) * acc_up, with a second weight (act: SiLU or GELU)
 };
 
 constexpr int TM = 64, TN = 64, TK = 16, PAD = 4;
@@ -20,7 +20,7 @@ constexpr int TM = 64, TN = 64, TK = 16, PAD = 4;
 template <typename TA, typename TW, typename TO, int MODE>
 __global__ void __launch_bounds__(256)
 gemm_nt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, const TW* __restrict__ W2,
-               TO* __restrict__ out, int ldo, int M, int N, int K) {
+               TO* __restrict__ out, int ldo, int M, int N, int K, const Ending e) {
     __shared__ float As[TK][TM + PAD];
     __shared__ float Ws[TK][TN + PAD];
     __shared__ float Ws2[MODE == kSwiGLU ? TK : 1][TN + PAD];
@@ -74,13 +74,13 @@ gemm_nt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, cons
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             TO* o = out + (size_t)m * ldo + n;
+            const float r = acc[i][j] + ending_bias(e.bias, e.bias_dtype, n);
             if (MODE == kStore) {
-                *o = from_float<TO>(acc[i][j]);
+                *o = from_float<TO>(r);
             } else if (MODE == kAccumulate) {
-                *o = from_float<TO>(to_float(*o) + acc[i][j]);
+                *o = from_float<TO>(to_float(*o) + r);
             } else {
-                const float g = acc[i][j];
-                *o = from_float<TO>(g / (1.0f + expf(-g)) * acc2[i][j]);
+                *o = from_float<TO>(gate_activation(r, e.act) * (acc2[i][j] + ending_bias(e.bias2, e.bias_dtype, n)));
             }
         }
     }
@@ -88,14 +88,14 @@ gemm_nt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, cons
 
 template <typename TA, typename TW, typename TO>
 static int launch_gemm(int mode, const void* A, int lda, const void* W, const void* W2, void* out, int ldo,
-                       int M, int N, int K, cudaStream_t stream) {
+                       int M, int N, int K, const Ending& e, cudaStream_t stream) {
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     if (mode == kStore)
-        gemm_nt_kernel<TA, TW, TO, kStore><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, nullptr, (TO*)out, ldo, M, N, K);
+        gemm_nt_kernel<TA, TW, TO, kStore><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, nullptr, (TO*)out, ldo, M, N, K, e);
     else if (mode == kAccumulate)
-        gemm_nt_kernel<TA, TW, TO, kAccumulate><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, nullptr, (TO*)out, ldo, M, N, K);
+        gemm_nt_kernel<TA, TW, TO, kAccumulate><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, nullptr, (TO*)out, ldo, M, N, K, e);
     else if (mode == kSwiGLU)
-        gemm_nt_kernel<TA, TW, TO, kSwiGLU><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, (const TW*)W2, (TO*)out, ldo, M, N, K);
+        gemm_nt_kernel<TA, TW, TO, kSwiGLU><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, (const TW*)W2, (TO*)out, ldo, M, N, K, e);
     else
         return fail("gemm_simt: unknown mode %d", mode);
     MDMA_LAUNCH_OK("gemm_simt");
@@ -108,17 +108,20 @@ using namespace mdma;
 
 extern "C" int mdma_gemm_simt(int mode, const void* A, int a_dtype, int lda, const void* W, const void* W2,
                               int w_dtype, void* out, int out_dtype, int ldo, int M, int N, int K,
-                              cudaStream_t stream) {
+                              const void* bias, const void* bias2, int bias_dtype, int act, cudaStream_t stream) {
     MDMA_REQUIRE(M >= 0 && N > 0 && K > 0 && lda >= K && ldo >= N, "gemm_simt: bad sizes M=%d N=%d K=%d lda=%d ldo=%d", M, N, K, lda, ldo);
     MDMA_REQUIRE(mode != kSwiGLU || W2 != nullptr, "gemm_simt: SwiGLU needs two weights");
     MDMA_REQUIRE(mode != kAccumulate || out_dtype == kF32, "gemm_simt: the residual stream is float");
     MDMA_REQUIRE((size_t)((M + TM - 1) / TM) <= 65535, "gemm_simt: too many rows (%d)", M);
+    MDMA_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_simt: unknown activation %d", act);
+    MDMA_REQUIRE(bias_dtype == kF32 || bias_dtype == kBF16, "gemm_simt: unknown bias dtype %d", bias_dtype);
     if (M == 0) return 0;
+    const Ending e{bias, mode == kSwiGLU ? bias2 : nullptr, bias_dtype, act};
     if (a_dtype == kF32 && w_dtype == kF32 && out_dtype == kF32)
-        return launch_gemm<float, float, float>(mode, A, lda, W, W2, out, ldo, M, N, K, stream);
+        return launch_gemm<float, float, float>(mode, A, lda, W, W2, out, ldo, M, N, K, e, stream);
     if (a_dtype == kBF16 && w_dtype == kBF16 && out_dtype == kBF16)
-        return launch_gemm<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(mode, A, lda, W, W2, out, ldo, M, N, K, stream);
+        return launch_gemm<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(mode, A, lda, W, W2, out, ldo, M, N, K, e, stream);
     if (a_dtype == kBF16 && w_dtype == kBF16 && out_dtype == kF32)
-        return launch_gemm<__nv_bfloat16, __nv_bfloat16, float>(mode, A, lda, W, W2, out, ldo, M, N, K, stream);
+        return launch_gemm<__nv_bfloat16, __nv_bfloat16, float>(mode, A, lda, W, W2, out, ldo, M, N, K, e, stream);
     return fail("gemm_simt: unsupported dtypes a=%d w=%d out=%d", a_dtype, w_dtype, out_dtype);
 }

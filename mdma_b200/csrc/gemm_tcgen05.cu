@@ -38,6 +38,7 @@ struct TcParams {
     float* partial;            // [splits, n_tokens, n_features] when MODE == kTcPartial
     int* status;               // device word set non-zero when a wait ran out
     int cluster;               // > 1: that many blocks of a cluster split K and reduce through shared memory
+    Ending ending;             // bias vectors over the features and the gate's activation
     float* sk_partial;         // block-pair kernel: one partial tile per pair and block, for tiles shared by two pairs
     int* sk_flags;             // [pairs * 2] zero between launches; non-null switches the even K-block split on
 };
@@ -200,6 +201,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp >= 2 && rank == 0 && (acc_ok || p.cluster > 1)) {
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         const float* staged = reinterpret_cast<const float*>(base_ptr) + quad * 32 + lane;
+        // the bias goes in once: with partial sums, into the first split's
+        const bool biased = f < p.n_features && (MODE != kTcPartial || blockIdx.z == 0);
+        const float b1 = biased ? ending_bias(p.ending.bias, p.ending.bias_dtype, f) : 0.f;
+        const float b2 = kDual && biased ? ending_bias(p.ending.bias2, p.ending.bias_dtype, f) : 0.f;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 16) {
             if (t0 + c >= p.n_tokens) break;           // uniform over the warp
@@ -227,14 +232,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; ++j) old[j] = j < valid ? o[(size_t)j * p.ldo] : 0.f;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) if (j < valid) o[(size_t)j * p.ldo] = old[j] + v[j];
+                    for (int j = 0; j < 16; ++j) if (j < valid) o[(size_t)j * p.ldo] = old[j] + (v[j] + b1);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         if (j >= valid) break;
                         const int t = t0 + c + j;
-                        float r = v[j];
-                        if (MODE == kTcSwiGLU) r = r / (1.0f + __expf(-r)) * u[j];
+                        float r = v[j] + b1;
+                        if (MODE == kTcSwiGLU) r = gate_activation_fast(r, p.ending.act) * (u[j] + b2);
                         if (MODE == kTcPartial) {
                             p.partial[((size_t)blockIdx.z * p.n_tokens + t) * p.n_features + f] = r;
                         } else if (p.out_f32) {
@@ -443,6 +448,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             const int buf = si % kBufs;
             const int f = (sg.tile / t_tiles) * 256 + rank * 128 + row;
             const int t0 = (sg.tile % t_tiles) * BN;
+            const float b1 = f < p.n_features ? ending_bias(p.ending.bias, p.ending.bias_dtype, f) : 0.f;
+            const float b2 = kDual && f < p.n_features ? ending_bias(p.ending.bias2, p.ending.bias_dtype, f) : 0.f;
             ok = __all_sync(0xffffffffu, ptx::mbar_wait(acc_full(buf), (si / kBufs) & 1, abort_flag));
             if (!ok) break;
             ptx::tc_fence_after_sync();
@@ -495,14 +502,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                         for (int q = 0; q < 16; ++q) old[q] = q < valid ? o[(size_t)q * p.ldo] : 0.f;
 #pragma unroll
-                        for (int q = 0; q < 16; ++q) if (q < valid) o[(size_t)q * p.ldo] = old[q] + v[q];
+                        for (int q = 0; q < 16; ++q) if (q < valid) o[(size_t)q * p.ldo] = old[q] + (v[q] + b1);
                     } else {
 #pragma unroll
                         for (int q = 0; q < 16; ++q) {
                             if (q >= valid) break;
                             const int t = t0 + c + q;
-                            float r = v[q];
-                            if (MODE == kTcSwiGLU) r = r / (1.0f + __expf(-r)) * u[q];
+                            float r = v[q] + b1;
+                            if (MODE == kTcSwiGLU) r = gate_activation_fast(r, p.ending.act) * (u[q] + b2);
                             if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + f] = r;
                             else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(r);
                         }
@@ -837,7 +844,7 @@ int mdma_splitk_reduce(int mode, const float* partial, int splits, int n_tokens,
 int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2, void* out, int out_f32,
                  int ldo, int n_tokens, int n_features, int K, int bn, int splits, float* scratch,
                  long scratch_floats, int* status, int defer_reduce, int* splits_used, int* sk_flags,
-                 cudaStream_t stream) {
+                 const void* bias, const void* bias2, int bias_dtype, int act, cudaStream_t stream) {
     if (splits_used) *splits_used = 1;
     MDMA_REQUIRE(n_tokens >= 0 && n_features > 0 && K > 0, "gemm_tc: bad sizes");
     MDMA_REQUIRE(K % 8 == 0, "gemm_tc: K=%d is not a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
@@ -845,6 +852,9 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     MDMA_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && (!w2 || ((uintptr_t)w2 & 15) == 0),
                  "gemm_tc: operands must be 16-byte aligned");
     MDMA_REQUIRE(mode != kTcSwiGLU || w2, "gemm_tc: SwiGLU needs two weights");
+    MDMA_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_tc: unknown activation %d", act);
+    MDMA_REQUIRE(bias_dtype == kF32 || bias_dtype == kBF16, "gemm_tc: unknown bias dtype %d", bias_dtype);
+    const Ending ending{bias, mode == kTcSwiGLU ? bias2 : nullptr, bias_dtype, act};
     MDMA_REQUIRE(mode != kTcAccumulate || out_f32, "gemm_tc: the residual stream is float");
     MDMA_REQUIRE(mode >= 0 && mode <= 2, "gemm_tc: unknown mode %d", mode);
     MDMA_REQUIRE(bn == 512 || (n_tokens + bn - 1) / bn <= 65535, "gemm_tc: too many token tiles");
@@ -860,6 +870,7 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
         pc.n_tokens = n_tokens; pc.n_features = n_features; pc.k_blocks = k_blocks;
         pc.kb_per_split = (k_blocks + c - 1) / c;
         pc.partial = nullptr; pc.status = status; pc.cluster = c; pc.sk_partial = nullptr; pc.sk_flags = nullptr;
+        pc.ending = ending;
         if (mode == kTcStore) return run_tc_bn<kTcStore>(bn, x, ldx, w, w2, K, pc, 1, stream);
         if (mode == kTcAccumulate) return run_tc_bn<kTcAccumulate>(bn, x, ldx, w, w2, K, pc, 1, stream);
         return run_tc_bn<kTcSwiGLU>(bn, x, ldx, w, w2, K, pc, 1, stream);
@@ -873,6 +884,7 @@ int mdma_gemm_tc(int mode, const void* x, int ldx, const void* w, const void* w2
     p.kb_per_split = (k_blocks + splits - 1) / splits;
     splits = (k_blocks + p.kb_per_split - 1) / p.kb_per_split;     // no empty split
     p.partial = nullptr; p.status = status; p.cluster = 1; p.sk_partial = nullptr; p.sk_flags = nullptr;
+    p.ending = ending;
     if (bn == 512) {           // the two-block kernel (a pair covers 256 features x 256 tokens)
         // scratch: one partial tile per block of every pair (accumulators x 256 x 128 floats each); the flags,
         // one per block, are zero between launches

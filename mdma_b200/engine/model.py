@@ -91,7 +91,8 @@ class DecoderModel:
     def lay_out_weights(self, expected: dict[str, TensorSpec], held_dtype, take) -> dict:
         """Where every tensor lives: `take(shape, dtype)` hands out (zeroed) device memory, or None
         when only sizes are wanted.  Tensors that a part wants as rows of one matrix (`fused_tensors`)
-        get one region, the pieces are views of its rows; the whole is returned under its own name.
+        (or as pieces of one vector) get one region, the pieces are views of its rows; the whole is returned
+        under its own name.
         `held_dtype(name, spec)` is the dtype a tensor is kept in."""
         tensors: dict = {}
         for part in self.all_parts():
@@ -102,10 +103,12 @@ class DecoderModel:
                     continue          # placed already (a part that runs at two places of the schedule)
                 specs = [expected[n] for n in names]
                 dtypes = {held_dtype(n, s) for n, s in zip(names, specs)}
-                if any(len(s.shape) != 2 or s.shape[1] != specs[0].shape[1] for s in specs) or len(dtypes) != 1:
-                    raise ValueError(f"{whole_name}: only matrices of one width and dtype can share a matrix")
+                if (len(specs[0].shape) not in (1, 2) or any(tuple(s.shape[1:]) != tuple(specs[0].shape[1:]) for s in specs)
+                        or len(dtypes) != 1):
+                    raise ValueError(f"{whole_name}: only matrices of one width (or vectors) of one dtype can be "
+                                     f"laid out as one")
                 rows = sum(s.shape[0] for s in specs)
-                t = take((rows, specs[0].shape[1]), dtypes.pop())
+                t = take((rows,) + tuple(specs[0].shape[1:]), dtypes.pop())
                 tensors[whole_name] = t
                 r = 0
                 for n, sp in zip(names, specs):

@@ -106,7 +106,7 @@ def main(argv=None) -> int:
 
     def gate_up_only(i):
         f = blocks[i % C].ffn
-        f.gate_up.swiglu(h, ctx.buf("act", f.inner), B)
+        f.gate_up.gated(h, ctx.buf("act", f.inner), B)
 
     def down_only(i):
         f = blocks[i % C].ffn

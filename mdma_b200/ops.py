@@ -103,9 +103,25 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
           ctypes.c_long(split_stride), _stream())
 
 
+ACT_SILU, ACT_GELU_TANH = 0, 1
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+
+
+def ending_args(n_features: int, bias: Optional[torch.Tensor], bias2: Optional[torch.Tensor], act: int):
+    """The four arguments by which the product kernels take their bias vectors and the gate's activation."""
+    for b in (bias, bias2):
+        if b is not None:
+            assert b.is_cuda and b.is_contiguous() and b.shape == (n_features,)
+            assert bias.dtype == b.dtype and b.dtype in (torch.float32, torch.bfloat16)
+    assert bias2 is None or bias is not None
+    return _ptr(bias), _ptr(bias2), _i(dtype_code(bias.dtype) if bias is not None else F32), _i(act)
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = GEMM_STORE,
-              w2: Optional[torch.Tensor] = None, m: Optional[int] = None) -> None:
-    """out[:m] (=, +=) a[:m] @ w.T on the CUDA cores; SwiGLU mode takes gate=w, up=w2."""
+              w2: Optional[torch.Tensor] = None, m: Optional[int] = None, bias: Optional[torch.Tensor] = None,
+              bias2: Optional[torch.Tensor] = None, act: int = ACT_SILU) -> None:
+    """out[:m] (=, +=) a[:m] @ w.T (+ bias) on the CUDA cores; the gated mode takes gate=w, up=w2 and
+    gives act(gate) * up."""
     _need_cuda(a, w, out, w2)
     assert a.dim() == 2 and w.dim() == 2 and out.dim() == 2
     assert a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
@@ -116,7 +132,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = G
         assert w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous()
     _call("core", "mdma_gemm_simt", _i(mode), _ptr(a), _i(dtype_code(a.dtype)), _i(a.stride(0)),
           _ptr(w), _ptr(w2), _i(dtype_code(w.dtype)), _ptr(out), _i(dtype_code(out.dtype)),
-          _i(out.stride(0)), _i(M), _i(N), _i(K), _stream())
+          _i(out.stride(0)), _i(M), _i(N), _i(K), *ending_args(N, bias, bias2, act), _stream())
 
 
 def rope_cache_write(qkv: torch.Tensor, n_tokens: int, tok_seq, tok_pos, seq_slot, inv_freq,

@@ -166,8 +166,10 @@ def take_pending(target: torch.Tensor, mode: int, rows: int, st: Optional[Tensor
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GEMM_STORE,
          w2: Optional[torch.Tensor] = None, m: Optional[int] = None,
          bn: Optional[int] = None, splits: Optional[int] = None, defer: bool = False,
-         st: Optional[TensorState] = None) -> None:
-    """out[:m] (=, +=) a[:m] @ w.T on the tensor cores; SwiGLU mode takes gate=w, up=w2.
+         st: Optional[TensorState] = None, bias: Optional[torch.Tensor] = None,
+         bias2: Optional[torch.Tensor] = None, act: int = ops.ACT_SILU) -> None:
+    """out[:m] (=, +=) a[:m] @ w.T (+ bias) on the tensor cores; the gated mode takes gate=w, up=w2 and
+    gives act(gate) * up.
     `defer`: if the product is split over K, leave its partial sums for the next kernel
     (a norm or the rotary write) to add up; see `take_pending`.  `st`: the engine's state."""
     _need_cuda(a, w, out, w2)
@@ -193,7 +195,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
     _call("tensor", "mdma_gemm_tc", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), _ptr(out),
           _i(int(out.dtype == torch.float32)), _i(out.stride(0)), _i(M), _i(N), _i(K), _i(bn), _i(splits),
           _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status),
-          _i(int(defer)), ctypes.byref(used), _ptr(st.sk_flags) if EVEN_SPLIT else None, _stream(),
+          _i(int(defer)), ctypes.byref(used), _ptr(st.sk_flags) if EVEN_SPLIT else None,
+          *ops.ending_args(N, bias, bias2, act), _stream(),
           launches=1 if (splits == 1 or defer) else 2)
     if defer and used.value > 1:
         st.pending = Pending(out, mode, used.value, M, N)

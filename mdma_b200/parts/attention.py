@@ -1,6 +1,6 @@
 """Grouped-query causal attention over the cache.
 
-q, k, v = h Wq^T, h Wk^T, h Wv^T (no biases); q and k take the position
+q, k, v = h Wq^T, h Wk^T, h Wv^T (no biases unless `bias` is set); q and k take the position
 encoding, k and v go to the cache; a query at position p reads the keys
 [first, p] of its own sequence (first = 0, or p+1-window), kv head = q head //
 (heads / kv heads), scores (q.k) * scale through a float softmax; the result
@@ -39,6 +39,7 @@ class Attention(Part):
         self.scale = float(p["scale"])
         self.window = int(p.get("window", 0) or 0)
         self.shared_cache = bool(p.get("shared_cache", False))
+        self.bias = bool(p.get("bias", False))              # a vector added after each of the four products
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"{self.n_heads} heads do not divide over {self.n_kv_heads} kv heads")
         pos = p["position"]
@@ -56,6 +57,9 @@ class Attention(Part):
             specs["k_proj.weight"] = TensorSpec((self.kv_width, self.hidden))
             specs["v_proj.weight"] = TensorSpec((self.kv_width, self.hidden))
         specs["o_proj.weight"] = TensorSpec((self.hidden, self.q_width))
+        if self.bias:
+            for name in [n for n in specs]:
+                specs[name[:-len("weight")] + "bias"] = TensorSpec((specs[name].shape[0],), "vector", "normal")
         return specs
 
     MAX_HEAD_DIM = 256        # the plain attention kernel's limit (csrc/attention_simple.cu)
@@ -68,7 +72,12 @@ class Attention(Part):
 
     def fused_tensors(self):
         # one product for q, k and v
-        return {} if self.shared_cache else {"qkv_proj.weight": ("q_proj.weight", "k_proj.weight", "v_proj.weight")}
+        if self.shared_cache:
+            return {}
+        fused = {"qkv_proj.weight": ("q_proj.weight", "k_proj.weight", "v_proj.weight")}
+        if self.bias:
+            fused["qkv_proj.bias"] = ("q_proj.bias", "k_proj.bias", "v_proj.bias")
+        return fused
 
     def kv_need(self):
         return KVNeed(self.n_kv_heads, self.head_dim, self.window)
@@ -91,12 +100,20 @@ class Attention(Part):
             # bound by hand with three separate matrices: rows [q heads | k heads | v heads]
             fused = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
                                tensors["v_proj.weight"]], dim=0).contiguous()
+        fused_bias = None
+        if self.bias:
+            if self.shared_cache:
+                fused_bias = tensors["q_proj.bias"]
+            elif "qkv_proj.bias" in tensors:
+                fused_bias = tensors["qkv_proj.bias"]
+            else:
+                fused_bias = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]).contiguous()
         self._fast_ok = False
         if rt.attention == "fast":
             from .. import ops_tensor
             self._fast_ok = ops_tensor.attention_supported(self.n_heads, self.n_kv_heads, self.head_dim)
-        self.qkv_proj = Linear(fused, rt)
-        self.o_proj = Linear(tensors["o_proj.weight"], rt)
+        self.qkv_proj = Linear(fused, rt, bias=fused_bias)
+        self.o_proj = Linear(tensors["o_proj.weight"], rt, bias=tensors.get("o_proj.bias"))
 
     def forward(self, ctx, h, x, view, owns_cache=True):
         n = ctx.n_tokens
@@ -142,4 +159,4 @@ class Attention(Part):
                                                   self.position.rotary_table()[1]))
 
     def resident_tensors(self):
-        return [self.qkv_proj.w, self.o_proj.w]
+        return [t for t in (self.qkv_proj.w, self.o_proj.w, self.qkv_proj.bias, self.o_proj.bias) if t is not None]

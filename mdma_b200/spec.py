@@ -15,9 +15,15 @@ from typing import Any, Optional
 @dataclass(frozen=True)
 class TensorSpec:
     """One tensor a part needs. `kind` is 'matrix' (kept in the compute dtype),
-    'vector' (kept as stored: bfloat16 or float32) or 'int' (held as int32)."""
+    'vector' (kept as stored: bfloat16 or float32) or 'int' (held as int32).
+    `init` says what the seeded random mode puts there: 'normal', 'ones' or 'zeros'
+    (by default matrices are normal, vectors ones, integer tables zeros)."""
     shape: tuple
     kind: str = "matrix"
+    init: str = ""
+
+    def initial(self) -> str:
+        return self.init or {"matrix": "normal", "vector": "ones", "int": "zeros"}[self.kind]
 
 
 @dataclass

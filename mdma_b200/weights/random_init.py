@@ -72,10 +72,12 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype,
     if out is not None:
         device, dtype = out.device, out.dtype
     device = torch.device(device) if device is not None else torch.device("cpu")
-    if spec.kind == "int":
-        t = torch.zeros(spec.shape, dtype=torch.int32, device=device)
-    elif spec.kind == "vector":
-        t = torch.ones(spec.shape, dtype=dtype, device=device)
+    how = spec.initial()
+    if how not in ("normal", "ones", "zeros"):
+        raise ValueError(f"{name}: unknown initialisation {how!r}")
+    if spec.kind == "int" or how != "normal":
+        t = (torch.ones if how == "ones" else torch.zeros)(
+            spec.shape, dtype=torch.int32 if spec.kind == "int" else dtype, device=device)
     elif device.type == "cuda":
         from .. import ops
         t = out if out is not None else torch.empty(spec.shape, dtype=dtype, device=device)

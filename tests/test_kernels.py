@@ -516,6 +516,64 @@ def test_gemm_tensor(M, N, K, mode):
     ops_tensor.check_status(torch.device(DEV))
 
 
+def _ending_reference(a, w, w2, b, b2, mode, act, x0):
+    ref = a.double() @ w.double().t() + b.double()
+    if mode == 0:
+        return ref
+    if mode == 1:
+        return x0.double() + ref
+    up = a.double() @ w2.double().t() + b2.double()
+    if act == 0:
+        return ref / (1 + torch.exp(-ref)) * up
+    return 0.5 * ref * (1 + torch.tanh(math.sqrt(2 / math.pi) * (ref + 0.044715 * ref ** 3))) * up
+
+
+@pytest.mark.parametrize("bias_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K,mode,act,kw", [
+    (7, 520, 2048, 0, 0, {}),                       # the plan splits K: the bias goes into the first partial sum only
+    (7, 520, 2048, 1, 0, {}),
+    (5, 300, 1024, 1, 0, dict(splits=-3)),          # K split inside a cluster
+    (17, 264, 1536, 2, 1, dict(splits=-2)),
+    (64, 264, 512, 2, 1, {}), (9, 200, 72, 2, 0, {}),
+    (300, 520, 1032, 0, 0, {}), (200, 136, 4096, 1, 0, {}),      # one block per tile with a K split (129-512 tokens)
+    (700, 264, 512, 1, 0, {}), (600, 384, 640, 2, 1, {}),        # block pairs
+])
+def test_gemm_tensor_bias_and_gate_activation(M, N, K, mode, act, kw, bias_dtype):
+    """out = a W^T + b (stored, or added to the residual stream), and act(a Wg^T + bg) * (a Wu^T + bu) with SiLU
+    or GELU as the gate: on every kernel and split of the tensor-core product."""
+    from mdma_b200 import ops_tensor
+    torch.manual_seed(N + K)
+    a = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    w2 = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    b = torch.randn(N, device=DEV).to(bias_dtype)
+    b2 = torch.randn(N, device=DEV).to(bias_dtype)
+    x0 = torch.randn(M + 1, N, device=DEV)
+    out = x0.clone() if mode == 1 else torch.full((M + 1, N), 9.0, device=DEV, dtype=torch.bfloat16)
+    ops_tensor.gemm(a, w, out, mode, w2 if mode == 2 else None, M, bias=b, bias2=b2 if mode == 2 else None, act=act, **kw)
+    ops_tensor.check_status(torch.device(DEV))
+    want = _ending_reference(a, w, w2, b, b2, mode, act, x0[:M])
+    close(out[:M], want, 1e-3 if mode == 1 else 2e-2, 0 if mode == 1 else 1e-2)
+    assert torch.equal(out[M:], x0[M:]) if mode == 1 else bool((out[M:] == 9.0).all())
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mode,act", [(0, 0), (1, 0), (2, 0), (2, 1)])
+def test_gemm_simt_bias_and_gate_activation(dt, mode, act):
+    ops = ops_mod()
+    M, N, K = 67, 130, 100
+    torch.manual_seed(mode)
+    a = (torch.randn(M, K, device=DEV) * 0.5).to(dt)
+    w, w2 = (torch.randn(N, K, device=DEV) * 0.1).to(dt), (torch.randn(N, K, device=DEV) * 0.1).to(dt)
+    b, b2 = torch.randn(N, device=DEV).to(dt), torch.randn(N, device=DEV).to(dt)
+    x0 = torch.randn(M, N, device=DEV)
+    out = x0.clone() if mode == 1 else torch.empty(M, N, device=DEV, dtype=dt)
+    ops.gemm_simt(a, w, out, mode, w2 if mode == 2 else None, M, b, b2 if mode == 2 else None, act)
+    want = _ending_reference(a, w, w2, b, b2, mode, act, x0)
+    tol = dict(atol=2e-5) if dt == torch.float32 else dict(atol=2e-2, rtol=1e-2)
+    close(out, want, **(tol if mode != 1 else dict(atol=1e-4 if dt == torch.float32 else 1e-3)))
+
+
 @pytest.mark.parametrize("splits", [2, 3, 7])
 def test_gemm_tensor_split_k_is_reproducible(splits):
     from mdma_b200 import ops_tensor

@@ -432,3 +432,94 @@ def test_a_block_arrangement_with_parts_of_its_own(tmp_path, dtype, tol):
         for row, (r, c) in enumerate(zip(ref, cut)):
             assert np.abs(out[row] - r[c + step]).max() < tol
     eng.check_status()
+
+
+# ---- the built-in parts with options that Llama does not use: biases after every product, a GELU gate ----------
+def register_toy_biased():
+    """Two ordinary layers whose attention has a bias vector after each of its four products and whose
+    feed-forward is gated by GELU (tanh form) with biases after its three: options of the parts, chosen by
+    an architecture that is registered from here."""
+    from mdma_b200.config import Architecture
+    from mdma_b200.registry import ARCHITECTURES
+    from mdma_b200.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    def describe(c):
+        norm = lambda prefix: PartSpec("rmsnorm", dict(width=E, eps=c["eps"]), prefix=prefix)
+        pos = PartSpec("rotary", dict(head_dim=D, rotary_dim=D, theta=c["theta"], layout="split_half", scaling=None))
+        layers = []
+        for i in range(2):
+            p = f"l{i}."
+            layers.append(LayerSpec(
+                "prenorm", norm(p + "n1."),
+                PartSpec("attention", dict(hidden_size=E, num_heads=H, num_kv_heads=K, head_dim=D, scale=D ** -0.5,
+                                           window=0, position=pos, bias=True), prefix=p + "attn."),
+                norm(p + "n2."),
+                PartSpec("gated_mlp", dict(hidden_size=E, intermediate_size=F, bias=True,
+                                           activation="gelu_tanh" if i == 0 else "silu"), prefix=p + "mlp.")))
+        return ModelSpec(hidden_size=E, vocab_size=V, max_positions=256,
+                         embedding=PartSpec("embedding", dict(vocab_size=V, width=E), prefix="emb."),
+                         layers=layers, schedule=[ScheduleEntry(0), ScheduleEntry(1)], final_norm=norm("final."),
+                         lm_head=PartSpec("lm_head", dict(vocab_size=V, width=E), prefix="head."))
+
+    ARCHITECTURES.register("ToyBiasedLM", Architecture("ToyBiasedLM", lambda d: dict(d), describe), replace=True)
+
+
+def plain_toy_biased(c, W, ids):
+    W = {k: v.double() for k, v in W.items()}
+    T = len(ids)
+    x = W["emb.weight"][torch.tensor(ids)]
+    inv = plain_inv_freq(D, c["theta"], None)
+    pos = torch.arange(T)
+    lin = lambda h, name: h @ W[name + ".weight"].t() + W[name + ".bias"]
+    for i in range(2):
+        p = f"l{i}."
+        h = plain_rmsnorm(x, W[p + "n1.weight"], c["eps"])
+        q = plain_rope(lin(h, p + "attn.q_proj").reshape(T, H, D), pos, inv, "split_half")
+        k = plain_rope(lin(h, p + "attn.k_proj").reshape(T, K, D), pos, inv, "split_half")
+        v = lin(h, p + "attn.v_proj").reshape(T, K, D)
+        x = x + lin(plain_attention(q, k, v, D ** -0.5), p + "attn.o_proj")
+        h = plain_rmsnorm(x, W[p + "n2.weight"], c["eps"])
+        g, u = lin(h, p + "mlp.gate_proj"), lin(h, p + "mlp.up_proj")
+        if i == 0:
+            act = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3))) * u
+        else:
+            act = plain_swiglu(g, u)
+        x = x + lin(act, p + "mlp.down_proj")
+    return plain_rmsnorm(x, W["final.weight"], c["eps"]) @ W["head.weight"].t()
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 8e-2)])
+def test_biases_and_another_gate_activation_are_options_of_the_parts(tmp_path, dtype, tol):
+    """The bias vectors are seeded like matrices (so that a missing one shows), laid out with q, k and v as one
+    vector beside the one matrix, added once however the product is split over K, and reach the attention
+    kernel that does the rotary encoding itself (single tokens) through the first partial sum."""
+    register_toy_biased()
+    from mdma_b200.engine import Engine, StepEntry
+    from mdma_b200.weights import write_random_model
+    from mdma_b200.weights.safetensors_io import SafetensorsFile
+    cfg = dict(architectures=["ToyBiasedLM"], eps=1e-5, theta=10000.0)
+    d = write_random_model(str(tmp_path / "toy4"), cfg, 5, torch.bfloat16 if dtype == "bfloat16" else torch.float32, std=0.08)
+    sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    W = {n: sf.tensor(n).clone().float() for n in sf.entries}
+    assert W["l0.attn.q_proj.bias"].shape == (H * D,) and float(W["l1.mlp.down_proj.bias"].abs().max()) > 0.05
+    eng = Engine(d, dtype=dtype, max_batch=2, max_context=128, logit_rows=128)
+    held = eng.held_bytes()
+    assert all(eng.memory_plan()[k] == v for k, v in held.items())         # the bias vectors are in the plan
+    g = torch.Generator().manual_seed(3)
+    seqs = [torch.randint(0, V, (n,), generator=g).tolist() for n in (70, 9)]
+    ref = [plain_toy_biased(cfg, W, s).numpy() for s in seqs]
+    # the biases matter: without them the logits differ by far more than the tolerance
+    W0 = {n: (torch.zeros_like(t) if n.endswith(".bias") else t) for n, t in W.items()}
+    assert np.abs(plain_toy_biased(cfg, W0, seqs[0]).numpy() - ref[0]).max() > 10 * tol
+    slots = [eng.acquire() for _ in seqs]
+    cut = [50, 3]
+    out = eng.step([StepEntry(sl, s[:c], list(range(c))) for sl, s, c in zip(slots, seqs, cut)]).cpu().numpy()
+    off = 0
+    for r, c in zip(ref, cut):
+        assert np.abs(out[off:off + c] - r[:c]).max() < tol
+        off += c
+    for step in range(6):
+        out = eng.step([StepEntry(sl, [s[c + step]], [0]) for sl, s, c in zip(slots, seqs, cut)]).cpu().numpy()
+        for row, (r, c) in enumerate(zip(ref, cut)):
+            assert np.abs(out[row] - r[c + step]).max() < tol
+    eng.check_status()
