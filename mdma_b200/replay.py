@@ -42,8 +42,17 @@ def main(argv=None) -> int:
     probe_cfg = json.load(open(os.path.join(args.model, "config.json")))
     max_context = min(int(probe_cfg.get("max_position_embeddings", max_tokens)), max_tokens)
     extra = {} if args.chunk_tokens is None else {"chunk_tokens": args.chunk_tokens}
+    # A step may want the logits of every token it brings, so the logits buffer has a row per token of the
+    # cache; but never more than a quarter of the free device memory (a step that wants more rows than
+    # that is refused with the engine's own error, not truncated).
+    import torch
+    logit_rows = max_tokens
+    vocab = int(probe_cfg.get("vocab_size", 0))
+    if vocab > 0 and torch.cuda.is_available():
+        free_bytes, _ = torch.cuda.mem_get_info()
+        logit_rows = max(64, min(max_tokens, (free_bytes // 4) // (4 * vocab)))
     engine = Engine(args.model, dtype=args.dtype, max_tokens=max_tokens, max_context=max_context,
-                    page_size=page, logit_rows=max_tokens, **extra)
+                    page_size=page, logit_rows=logit_rows, **extra)
     slots: dict = {}
     for line in sys.stdin:
         line = line.strip()
