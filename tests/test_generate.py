@@ -441,6 +441,38 @@ def test_the_benchmark_layer_shape_in_bfloat16_against_true_32_bit(lengths):
     assert (np.sqrt((err ** 2).mean(1)) / a.std(1)).max() < 0.03
 
 
+def test_long_prompts_at_the_benchmark_layer_shape_against_true_32_bit():
+    """The same two layers with prompts of 2,500, 700 and 130 tokens: a first step of all but the last 64
+    tokens as passes of 1,024 (the tcgen05 attention over dozens of key blocks, some of them cached by an
+    earlier pass; block-pair products over many token tiles), a step of 56 tokens on that prefix, then eight
+    steps of one token, the longest sequence beyond 2,048 positions (keys split over blocks).  Against the
+    float32 engine, whose weights are not rounded: measured 0.116 at most on logits of deviation 1.28 and
+    1.9 % of a row's deviation in the root mean square, the same on every row."""
+    import numpy as np
+    import bench
+    from mdma_b200.engine import Engine, StepEntry
+    cfg = dict(bench.LLAMA_31_8B, num_hidden_layers=2, max_position_embeddings=4096)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in (2500, 700, 130)]
+    res = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(config=cfg, seed=0, dtype=dtype, max_batch=3, max_context=2688, logit_rows=32, chunk_tokens=1024)
+        slots = [eng.acquire() for _ in prompts]
+        wants = lambda p: [0, len(p) // 3, len(p) // 2, len(p) - 2, len(p) - 1]
+        out = [eng.step([StepEntry(s, p[:-64], wants(p[:-64])) for s, p in zip(slots, prompts)]).cpu().numpy().copy()]
+        out.append(eng.step([StepEntry(s, p[-64:-8], [0, 55]) for s, p in zip(slots, prompts)]).cpu().numpy().copy())
+        for j in range(8):
+            out.append(eng.step([StepEntry(s, [p[len(p) - 8 + j]], [0]) for s, p in zip(slots, prompts)]).cpu().numpy().copy())
+        eng.check_status()
+        res[dtype] = np.concatenate(out).astype(np.float64)
+        del eng
+    a, b = res["float32"], res["bfloat16"]
+    assert a.shape[0] == 45 and np.isfinite(b).all() and 1.0 < a.std() < 1.6
+    err = np.abs(a - b)
+    assert err.max() < 0.2, err.max()
+    assert (np.sqrt((err ** 2).mean(1)) / a.std(1)).max() < 0.03
+
+
 def test_random_traffic_replayed_runs_equal_the_step_by_step_loop():
     """Random batches (1-9 prompts of 1 to context-5 tokens, budgets of 1-40 tokens, greedy or sampled with
     random options, random stop tokens, runs of 1, 3 or 8 replayed steps): the same tokens and finish
