@@ -197,7 +197,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
           _ptr(st.scratch), ctypes.c_long(st.scratch.numel()), _ptr(st.status),
           _i(int(defer)), ctypes.byref(used), _ptr(st.sk_flags) if EVEN_SPLIT else None,
           *ops.ending_args(N, bias, bias2, act), _stream(),
-          launches=1 if (splits == 1 or defer) else 2)
+          launches=2 if (splits > 1 and not defer) else 1)
     if defer and used.value > 1:
         st.pending = Pending(out, mode, used.value, M, N)
 
