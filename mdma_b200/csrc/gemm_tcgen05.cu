@@ -350,6 +350,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     auto acc_empty = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStages + 5);
+    const uint32_t ep_bar = bar0 + 8u * (2 * kStages + 6);      // this block's eight epilogue warps meet here (bounded)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = (int)ptx::cluster_rank();
@@ -364,6 +365,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(acc_full(b), 1); ptx::mbar_init(acc_empty(b), 16); }   // 8 epilogue warps x 2 blocks
+        ptx::mbar_init(ep_bar, 256);
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -443,6 +445,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         float* my_part = p.sk_partial ? p.sk_partial + ((size_t)pair * 2 + rank) * part_stride + row : nullptr;
         const float* prev_part = p.sk_partial && pair > 0 ? p.sk_partial + ((size_t)(pair - 1) * 2 + rank) * part_stride + row : nullptr;
         bool ok = true;
+        uint32_t ep_phase = 0;
         for (int si = 0; si < n_seg && ok; ++si) {
             const Segment sg = work.get(si);
             const int buf = si % kBufs;
@@ -522,8 +525,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             if (lane == 0) ptx::mbar_arrive_cluster(lead_empty[buf]);
             if (sg.kind == kSegHead || sg.kind == kSegTail) {
                 // the eight epilogue warps of this block: all partial rows written (read) before the flag moves
+                // (an mbarrier, not bar.sync: a warp that gave up elsewhere must not leave the others waiting for ever)
                 __threadfence();
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                ptx::mbar_arrive(ep_bar);
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait(ep_bar, ep_phase & 1u, abort_flag));
+                ++ep_phase;
+                if (!ok) break;
                 if (warp == 2 && lane == 0) {
                     int* flag = p.sk_flags + (size_t)(sg.kind == kSegHead ? pair : pair - 1) * 2 + rank;
                     const int v = sg.kind == kSegHead ? 1 : 0;          // set by the writer, cleared by the reader
