@@ -199,6 +199,22 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
         for (int sidx = 0; sidx < splits; ++sidx) a += prow[(size_t)sidx * split_stride + col];
         return a;
     };
+    // two columns at once, the partial sums fetched four splits at a time before they are added (in split
+    // order, as `load` adds them): the loads of a pair are in flight together instead of one after the other
+    auto load2 = [&](int c0, int c1, float& x0, float& x1) {
+        if (splits == 0) { x0 = to_float(row[c0]); x1 = to_float(row[c1]); return; }
+        float a = 0.f, b = 0.f;
+        int sidx = 0;
+        for (; sidx + 4 <= splits; sidx += 4) {
+            const float* q = prow + (size_t)sidx * split_stride;
+            const float a0 = q[c0], a1 = q[split_stride + c0], a2 = q[2 * split_stride + c0], a3 = q[3 * split_stride + c0];
+            const float b0 = q[c1], b1 = q[split_stride + c1], b2 = q[2 * split_stride + c1], b3 = q[3 * split_stride + c1];
+            a += a0; a += a1; a += a2; a += a3;
+            b += b0; b += b1; b += b2; b += b3;
+        }
+        for (; sidx < splits; ++sidx) { a += prow[(size_t)sidx * split_stride + c0]; b += prow[(size_t)sidx * split_stride + c1]; }
+        x0 = a; x1 = b;
+    };
     size_t cache_row = 0;
     if (write_kv) {
         const int slot = seq_slot[tok_seq[t]];
@@ -214,7 +230,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride,
     for (int i = threadIdx.x; i < (rot_end - h_lo) * half; i += blockDim.x) {
         const int h = h_lo + i / half, pr = i % half;
         const int d0 = interleaved ? 2 * pr : pr, d1 = interleaved ? 2 * pr + 1 : pr + half;
-        const float x0 = load(h * head_dim + d0), x1 = load(h * head_dim + d1);
+        float x0, x1;
+        load2(h * head_dim + d0, h * head_dim + d1, x0, x1);
         const float s = sc[pr], c = sc[half + pr];
         T* dst = h < n_heads ? row + (size_t)h * head_dim
                              : k_cache + (cache_row + (h - n_heads)) * head_dim;
