@@ -30,6 +30,29 @@ def test_greedy_generation_matches_the_plain_implementation():
         assert o.finish_reason == "length" and o.prompt_tokens == p
 
 
+@pytest.mark.parametrize("page", [16, 32, 128])
+def test_generation_with_other_page_sizes(page):
+    """Cache pages of 16, 32 and 128 rows (the decode kernel's tile loads want multiples of 32, the rotary
+    encoding inside it as well, the tcgen05 attention multiples of 64; what cannot be used gives way to another
+    kernel): float32 tokens equal the plain implementation's, the bfloat16 engine's replayed decode equals its
+    step-by-step loop, and graphs and eager steps agree across page boundaries."""
+    from mdma_b200.engine import Engine
+    d, c, tensors = make_model(TINY_B, 1, torch.bfloat16, std_scale=SHARP)
+    prompts = prompts_for(TINY_B, (5, 70, 33, 127), 3)
+    eng = Engine(d, dtype="float32", max_batch=4, max_context=256, page_size=page)
+    outs = eng.generate(prompts, max_tokens=40)
+    W = {k: v.float() for k, v in tensors.items()}
+    for p, o in zip(prompts, outs):
+        assert o.tokens == plain_generate(c, W, p, 40)
+    del eng
+    eng = Engine(d, dtype="bfloat16", max_batch=4, max_context=256, page_size=page)
+    a = eng.generate(prompts, max_tokens=40)
+    b = eng.generate(prompts, max_tokens=40, use_graphs=False)
+    assert [o.tokens for o in a] == [o.tokens for o in b]
+    eng.check_status()
+    eng.cache.check()
+
+
 def test_batches_one_after_another_and_stop_tokens():
     import mdma_b200
     d, c, tensors = make_model(TINY_C, 2, torch.float32)

@@ -1,6 +1,7 @@
 """Random schedules through `Engine.step` against the plain implementation: unequal batches, prompts whole or
 cut in random pieces on their cached prefix, single tokens, requests that end earlier, slots and pages used
-again, wanted places in any order, passes of 48 or 100 tokens, NaN in the cache rows that belong to nobody.
+again, wanted places in any order, passes of 48 or 100 tokens, cache pages of 16 to 128 rows, NaN in the cache rows
+that belong to nobody.
 A longer run of the same generator (13,000 steps) was made once by hand; this is its short form."""
 import random
 
@@ -24,9 +25,12 @@ def test_random_schedules(name, cfg, seed, wdtype, dtype):
     d, c, tensors = make_model(cfg, seed, wdtype, std_scale=SHARP)
     held = {k: (v.bfloat16().float() if dtype == "bfloat16" and v.dim() == 2 else v.float()) for k, v in tensors.items()}
     ctx = min(cfg["max_position_embeddings"], 260)
-    for trial in range(2):
+    for trial in range(3):
         chunk = (8192, 48, 100)[(trial + seed) % 3]
-        eng = Engine(d, dtype=dtype, max_batch=5, max_context=ctx, max_tokens=5 * 320, chunk_tokens=chunk, logit_rows=64)
+        # pages of 64 rows as everywhere, and once of 16, 32 or 128 (other tile loads, other kernels for some steps)
+        page = 64 if trial < 2 else (16, 32, 128, 32)[seed % 4]
+        eng = Engine(d, dtype=dtype, max_batch=5, max_context=ctx, max_tokens=5 * 384, chunk_tokens=chunk, logit_rows=64,
+                     page_size=page)
         g = torch.Generator().manual_seed(rnd.randrange(10 ** 6))
         for _batch in range(3):
             n = rnd.randint(1, 5)
