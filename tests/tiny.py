@@ -55,13 +55,23 @@ TINY_E = dict(
     tie_word_embeddings=True, max_position_embeddings=192)
 
 
-def make_model(cfg: dict, seed: int, dtype=torch.float32, root=None, std_scale: float = 1.0):
+def make_model(cfg: dict, seed: int, dtype=torch.float32, root=None, std_scale: float = 1.0, norm_jitter: float = 0.25):
     """Write a model folder into a fresh temporary directory; returns (dir, config dict, tensors).
-    Matrices are N(0, 0.02 * std_scale)."""
-    from mdma_b200.weights import write_random_model
+    Matrices are N(0, 0.02 * std_scale).  The random mode writes every norm weight as 1.0, which would hide
+    a norm that reads another layer's weight (or none): the folder is rewritten with norm weights
+    1 + norm_jitter * N(0, 1), different in every vector."""
+    from mdma_b200.weights import write_random_model, write_safetensors
     from mdma_b200.weights.safetensors_io import SafetensorsFile
     d = tempfile.mkdtemp(prefix="mdma_tiny_", dir=root)
     write_random_model(d, cfg, seed, dtype, std=0.02 * std_scale)
-    sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    path = os.path.join(d, "model.safetensors")
+    sf = SafetensorsFile(path)
     tensors = {n: sf.tensor(n).clone() for n in sf.entries}
+    del sf
+    if norm_jitter:
+        g = torch.Generator().manual_seed(1000 + seed)
+        for name in sorted(tensors):
+            if tensors[name].dim() == 1:
+                tensors[name] = (1.0 + norm_jitter * torch.randn(tensors[name].shape, generator=g)).to(tensors[name].dtype)
+        write_safetensors(path, tensors)
     return d, json.load(open(os.path.join(d, "config.json"))), tensors
