@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from plain_llama import plain_attention, plain_inv_freq, plain_rmsnorm, plain_rope, plain_swiglu
+from tiny import jitter_norm_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -132,6 +133,7 @@ def test_toy_architecture_builds_and_steps(tmp_path, dtype, tol):
     from mdma_b200.weights.safetensors_io import SafetensorsFile
     cfg = dict(architectures=["ToyMixedLM"], eps=1e-5, theta=5000.0, decay=0.8)
     d = write_random_model(str(tmp_path / "toy"), cfg, 7, torch.float32)
+    jitter_norm_weights(d, 7)          # norm weights that differ in every vector
     sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
     W = {n: sf.tensor(n).clone() for n in sf.entries}
     assert "l2.attn.k_proj.weight" not in W and "l1.mix.in.weight" in W     # the sharing layer owns no k/v
@@ -298,6 +300,7 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path):
     from mdma_b200.weights.safetensors_io import SafetensorsFile
     cfg = dict(architectures=["ToyRoutedLM"], eps=1e-5)
     d = write_random_model(str(tmp_path / "toy2"), cfg, 3, torch.float32)
+    jitter_norm_weights(d, 3)          # norm weights that differ in every vector
     sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
     W = {n: sf.tensor(n).clone() for n in sf.entries}
     W["l0.moe.router.weight"] = W["l0.moe.router.weight"] * 40      # decisive routing, all experts used
@@ -413,6 +416,7 @@ def test_a_block_arrangement_with_parts_of_its_own(tmp_path, dtype, tol):
     from mdma_b200.weights.safetensors_io import SafetensorsFile
     cfg = dict(architectures=["ToySandwichLM"], eps=1e-5, theta=10000.0)
     d = write_random_model(str(tmp_path / "toy3"), cfg, 4, torch.bfloat16 if dtype == "bfloat16" else torch.float32, std=0.08)
+    jitter_norm_weights(d, 4)          # norm weights that differ in every vector
     sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
     W = {n: sf.tensor(n).clone().float() for n in sf.entries}
     assert "l0.n3.weight" in W and "l1.n3.weight" not in W          # the loader learnt the extra tensors from the parts
@@ -499,6 +503,7 @@ def test_biases_and_another_gate_activation_are_options_of_the_parts(tmp_path, d
     from mdma_b200.weights.safetensors_io import SafetensorsFile
     cfg = dict(architectures=["ToyBiasedLM"], eps=1e-5, theta=10000.0)
     d = write_random_model(str(tmp_path / "toy4"), cfg, 5, torch.bfloat16 if dtype == "bfloat16" else torch.float32, std=0.08)
+    jitter_norm_weights(d, 5)          # norm weights that differ in every vector
     sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
     W = {n: sf.tensor(n).clone().float() for n in sf.entries}
     assert W["l0.attn.q_proj.bias"].shape == (H * D,) and float(W["l1.mlp.down_proj.bias"].abs().max()) > 0.05

@@ -55,23 +55,36 @@ TINY_E = dict(
     tie_word_embeddings=True, max_position_embeddings=192)
 
 
+def jitter_norm_weights(model_dir: str, seed: int, amount: float = 0.25) -> dict:
+    """Rewrite the folder's norm weights (the vectors that the random mode writes as 1.0) as 1 + amount * N(0, 1),
+    different in every vector; returns all tensors of the folder as they now are."""
+    from mdma_b200.weights import write_safetensors
+    from mdma_b200.weights.safetensors_io import SafetensorsFile
+    path = os.path.join(model_dir, "model.safetensors")
+    sf = SafetensorsFile(path)
+    tensors = {n: sf.tensor(n).clone() for n in sf.entries}
+    del sf
+    g = torch.Generator().manual_seed(1000 + seed)
+    for name in sorted(tensors):
+        t = tensors[name]
+        if t.dim() == 1 and t.is_floating_point() and bool((t == 1).all()):
+            tensors[name] = (1.0 + amount * torch.randn(t.shape, generator=g)).to(t.dtype)
+    write_safetensors(path, tensors)
+    return tensors
+
+
 def make_model(cfg: dict, seed: int, dtype=torch.float32, root=None, std_scale: float = 1.0, norm_jitter: float = 0.25):
     """Write a model folder into a fresh temporary directory; returns (dir, config dict, tensors).
     Matrices are N(0, 0.02 * std_scale).  The random mode writes every norm weight as 1.0, which would hide
     a norm that reads another layer's weight (or none): the folder is rewritten with norm weights
     1 + norm_jitter * N(0, 1), different in every vector."""
-    from mdma_b200.weights import write_random_model, write_safetensors
+    from mdma_b200.weights import write_random_model
     from mdma_b200.weights.safetensors_io import SafetensorsFile
     d = tempfile.mkdtemp(prefix="mdma_tiny_", dir=root)
     write_random_model(d, cfg, seed, dtype, std=0.02 * std_scale)
-    path = os.path.join(d, "model.safetensors")
-    sf = SafetensorsFile(path)
-    tensors = {n: sf.tensor(n).clone() for n in sf.entries}
-    del sf
     if norm_jitter:
-        g = torch.Generator().manual_seed(1000 + seed)
-        for name in sorted(tensors):
-            if tensors[name].dim() == 1:
-                tensors[name] = (1.0 + norm_jitter * torch.randn(tensors[name].shape, generator=g)).to(tensors[name].dtype)
-        write_safetensors(path, tensors)
+        tensors = jitter_norm_weights(d, seed, norm_jitter)
+    else:
+        sf = SafetensorsFile(os.path.join(d, "model.safetensors"))
+        tensors = {n: sf.tensor(n).clone() for n in sf.entries}
     return d, json.load(open(os.path.join(d, "config.json"))), tensors
