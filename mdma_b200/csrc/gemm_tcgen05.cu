@@ -792,12 +792,21 @@ int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_coun
         // 89.1 us and 29.5 against 32.9 us).  Two weight matrices (SwiGLU) stay with the pairs (61 against 95 us).
         const long pair_tiles = (long)((n_features + 255) / 256) * ((n_tokens + 255) / 256);
         if (mode != kTcSwiGLU && n_tokens <= 512 && pair_tiles * 10 < (long)(sm_count / 2) * 6) {
+            // Token tiles of 128, or of 256 where that puts more blocks on the SMs at once (O and down of 384
+            // tokens: 64 tiles of 256 x 2 splits against 96 tiles of 128).  Not for a product that is stored
+            // (QKV): alone it gains (256 tokens: 20.7 against 24.7 us with 3 splits), but the kernel that
+            // rotates and stores then reads three float partial sums per value and the step loses more.
             const int k_blocks = (K + kBK - 1) / kBK;
-            const long tiles = (long)((n_features + kBM - 1) / kBM) * ((n_tokens + 127) / 128);
-            int splits = (int)(sm_count / tiles);
-            if (splits > k_blocks / 4) splits = k_blocks / 4;
-            if (splits < 1) splits = 1;
-            *bn_out = 128; *splits_out = splits; return 0;
+            int best_bn = 128, best_splits = 1;
+            long best_blocks = 0;
+            for (int bn = 128; bn <= (mode == kTcAccumulate ? 256 : 128); bn *= 2) {
+                const long tiles = (long)((n_features + kBM - 1) / kBM) * ((n_tokens + bn - 1) / bn);
+                int splits = (int)(sm_count / tiles);
+                if (splits > k_blocks / 4) splits = k_blocks / 4;
+                if (splits < 1) splits = 1;
+                if (tiles * splits > best_blocks && tiles * splits <= sm_count) { best_blocks = tiles * splits; best_bn = bn; best_splits = splits; }
+            }
+            *bn_out = best_bn; *splits_out = best_splits; return 0;
         }
         *bn_out = 512; *splits_out = 1; return 0;
     }

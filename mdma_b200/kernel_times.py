@@ -2,6 +2,7 @@
 
     python -m mdma_b200.kernel_times [--batch 8] [--context 580] [--hidden 4096] [--intermediate 14336]
                                      [--heads 32] [--kv-heads 8] [--head-dim 128] [--vocab 128256]
+                                     [--bn 128 --splits 2]      (the products with another tile and split)
 
 An engine with `--copies` layers of these sizes is built with seeded random weights, its cache is filled
 to `--context` positions, and each kernel of a layer is called through the engine's own parts with the
@@ -50,6 +51,10 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--copies", type=int, default=6, help="layers (copies of weights and cache) that take turns")
     ap.add_argument("--repeat", type=int, default=48)
+    ap.add_argument("--bn", type=int, default=None,
+                    help="token tile of the four products instead of the plan's: 16...256 one block per tile, 512 block pairs")
+    ap.add_argument("--splits", type=int, default=None,
+                    help="K splits of the QKV, O and down products instead of the plan's (with --bn below 512)")
     a = ap.parse_args(argv)
 
     from . import ops
@@ -83,10 +88,20 @@ def main(argv=None) -> int:
     def settle():
         ops_tensor.flush_pending(eng.device, tc)
 
+    forced = dict(bn=a.bn, splits=a.splits if a.splits is not None else 1) if a.bn is not None else None
+
+    def product(lin, src, dst, mode):
+        # the part's own call, or (--bn/--splits) the same product with a tile and a split that the plan would not take
+        if forced is None:
+            lin._run(mode, src, dst, B, defer=True)
+        else:
+            kw = dict(forced, splits=1) if mode == ops.GEMM_SWIGLU else forced
+            ops_tensor.gemm(src, lin.w, dst, mode, lin.w2, B, defer=True, st=tc, **kw)
+        tc.pending = None                              # the partial sums stay where they are; nobody adds them here
+
     def qkv_only(i):
         m = blocks[i % C].mixer
-        m.qkv_proj.store(h, ctx.buf("qkv", m.row_width), B, defer=True)
-        tc.pending = None                              # the partial sums stay where they are; nobody adds them here
+        product(m.qkv_proj, h, ctx.buf("qkv", m.row_width), ops.GEMM_STORE)
 
     def attention_only(i):
         m = blocks[i % C].mixer
@@ -101,17 +116,15 @@ def main(argv=None) -> int:
 
     def o_only(i):
         m = blocks[i % C].mixer
-        m.o_proj.accumulate(ctx.buf("attn_out", m.q_width), x, B)
-        tc.pending = None
+        product(m.o_proj, ctx.buf("attn_out", m.q_width), x, ops.GEMM_ACCUMULATE)
 
     def gate_up_only(i):
         f = blocks[i % C].ffn
-        f.gate_up.gated(h, ctx.buf("act", f.inner), B)
+        product(f.gate_up, h, ctx.buf("act", f.inner), ops.GEMM_SWIGLU)
 
     def down_only(i):
         f = blocks[i % C].ffn
-        f.down.accumulate(ctx.buf("act", f.inner), x, B)
-        tc.pending = None
+        product(f.down, ctx.buf("act", f.inner), x, ops.GEMM_ACCUMULATE)
 
     n = a.repeat
     E, F, H, K, D, V = a.hidden, a.intermediate, a.heads, a.kv_heads, a.head_dim, a.vocab
