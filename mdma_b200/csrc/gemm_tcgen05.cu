@@ -39,6 +39,7 @@ struct TcParams {
     int* status;               // device word set non-zero when a wait ran out
     int cluster;               // > 1: that many blocks of a cluster split K and reduce through shared memory
     Ending ending;             // bias vectors over the features and the gate's activation
+    int pair_tokens;           // block-pair kernel: width of a token tile (a multiple of 32 up to 256)
     float* sk_partial;         // block-pair kernel: one partial tile per pair and block, for tiles shared by two pairs
     int* sk_flags;             // [pairs * 2] zero between launches; non-null switches the even K-block split on
 };
@@ -335,7 +336,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     using S = Tc2Smem<MODE>;
     constexpr int kStages = S::kStages;
     constexpr bool kDual = MODE == kTcSwiGLU;
-    constexpr int BN = 256;
+    constexpr int BN = 256;                                // the widest token tile; accumulators and partial tiles are laid out for it
+    const int bn = p.pair_tokens;                          // this launch's token tile: the tokens divided evenly over the fewest tiles
     constexpr int kAccs = kDual ? 2 : 1;
     constexpr int kBufs = kDual ? 1 : 2;                   // accumulator buffers of 256 (512) columns
     constexpr int kBufCols = kDual ? 512 : 256;
@@ -355,7 +357,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = (int)ptx::cluster_rank();
     const int n_pairs = gridDim.x / 2, pair = blockIdx.x / 2;
-    const int f_tiles = (p.n_features + 255) / 256, t_tiles = (p.n_tokens + BN - 1) / BN;
+    const int f_tiles = (p.n_features + 255) / 256, t_tiles = (p.n_tokens + bn - 1) / bn;
     const PairWork work = pair_work(pair, n_pairs, f_tiles * t_tiles, p.k_blocks, p.sk_flags != nullptr);
     const int n_seg = work.count();
 
@@ -388,13 +390,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         for (int si = 0; si < n_seg && ok; ++si) {
             const Segment sg = work.get(si);
             const int f0 = (sg.tile / t_tiles) * 256 + rank * 128;      // token tiles of one feature tile run together
-            const int t0 = (sg.tile % t_tiles) * BN + rank * 128;
+            const int t0 = (sg.tile % t_tiles) * bn + rank * (bn / 2);       // each block loads half of the token tile
+            const uint32_t stage_bytes = (uint32_t)(S::kA * (kDual ? 2 : 1) + (bn / 2) * kBK * 2);
             for (int i = sg.kb0; i < sg.kb1; ++i, ++it) {
                 const int s = it % kStages;
                 if (!ptx::mbar_wait(empty_bar(s), ((it / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 const uint32_t stage = base + s * S::kStage;
                 const uint32_t lead_full = ptx::cluster_map(full_bar(s), 0);
-                if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 2 * S::kStage);       // both blocks' bytes
+                if (rank == 0) ptx::mbar_expect_tx(full_bar(s), 2 * stage_bytes);     // both blocks' bytes
                 const int k = i * kBK;
                 ptx::tma_load_2d_pair(stage, &map_w, lead_full, k, f0);
                 if (kDual) ptx::tma_load_2d_pair(stage + S::kA, &map_w2, lead_full, k, f0);
@@ -403,7 +406,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ---- MMA issuer (leading block only) ----------------------------------------------
-        constexpr uint32_t idesc = ptx::idesc_bf16_f32(256, BN);
+        const uint32_t idesc = ptx::idesc_bf16_f32(256, bn);
         int it = 0;
         bool ok = true;
         for (int si = 0; si < n_seg && ok; ++si) {
@@ -438,7 +441,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // ---- epilogue: each block handles its own 128 features x 256 tokens of every segment ------
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                   // feature row within this block's half
-        const int c_begin = ((warp - 2) >> 2) * (BN / 2), c_end = c_begin + BN / 2;     // this warp's columns
+        const int c_begin = ((warp - 2) >> 2) * (bn / 2), c_end = c_begin + bn / 2;     // this warp's columns
         const uint32_t lead_empty[2] = {ptx::cluster_map(acc_empty(0), 0), ptx::cluster_map(acc_empty(1), 0)};
         // partial tiles in global memory: [pair][block of the pair][accumulator][column][128 rows]
         const size_t part_stride = (size_t)kAccs * BN * 128;
@@ -450,7 +453,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             const Segment sg = work.get(si);
             const int buf = si % kBufs;
             const int f = (sg.tile / t_tiles) * 256 + rank * 128 + row;
-            const int t0 = (sg.tile % t_tiles) * BN;
+            const int t0 = (sg.tile % t_tiles) * bn;
             const float b1 = f < p.n_features ? ending_bias(p.ending.bias, p.ending.bias_dtype, f) : 0.f;
             const float b2 = kDual && f < p.n_features ? ending_bias(p.ending.bias2, p.ending.bias_dtype, f) : 0.f;
             ok = __all_sync(0xffffffffu, ptx::mbar_wait(acc_full(buf), (si / kBufs) & 1, abort_flag));
@@ -705,7 +708,11 @@ static int run_tc2(const void* x, int ldx, const void* w, const void* w2, int K,
     mw2 = mw;
     if (MODE == kTcSwiGLU)
         if (int rc = make_map_2d(&mw2, w2, (uint64_t)p.n_features, (uint64_t)K, (uint64_t)K * 2, kBM)) return rc;
-    if (int rc = make_map_2d(&mx, x, (uint64_t)p.n_tokens, (uint64_t)K, (uint64_t)ldx * 2, 128)) return rc;
+    // token tiles of up to 256, all of one width: the tokens divided evenly over the fewest tiles (320 tokens: two
+    // tiles of 160, not one of 256 and one that is three quarters empty)
+    const int t_tiles = (p.n_tokens + 255) / 256;
+    p.pair_tokens = (((p.n_tokens + t_tiles - 1) / t_tiles) + 31) / 32 * 32;
+    if (int rc = make_map_2d(&mx, x, (uint64_t)p.n_tokens, (uint64_t)K, (uint64_t)ldx * 2, p.pair_tokens / 2)) return rc;
     p.cluster = 1;
     cudaLaunchConfig_t cfg = {};
     // persistent: one pair per two SMs at most
@@ -716,7 +723,7 @@ static int run_tc2(const void* x, int ldx, const void* w, const void* w2, int K,
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count < 2) sm_count = 2;
     }
-    const long tiles = (long)((p.n_features + 255) / 256) * ((p.n_tokens + 255) / 256);
+    const long tiles = (long)((p.n_features + 255) / 256) * ((p.n_tokens + p.pair_tokens - 1) / p.pair_tokens);
     const int pairs = (int)(tiles < sm_count / 2 ? tiles : sm_count / 2);
     cfg.gridDim = dim3(pairs * 2, 1, 1);
     cfg.blockDim = dim3(kTc2Threads); cfg.dynamicSmemBytes = S::kBytes; cfg.stream = stream;
