@@ -624,9 +624,11 @@ def test_gemm_tensor_cluster_split(cluster, M, N, K, mode):
                                         # more tiles than block pairs: every pair walks over several tiles
                                         (1100, 5000, 256, 0), (1100, 5000, 256, 1), (1100, 5000, 256, 2), (2300, 8200, 192, 1),
                                         # tiles shared by two pairs (K blocks split evenly), several K blocks per part
-                                        (1100, 5000, 1032, 0), (1100, 5000, 1032, 1), (700, 9000, 2048, 2), (2048, 4096, 4096, 0)])
+                                        (1100, 5000, 1032, 0), (1100, 5000, 1032, 1), (700, 9000, 2048, 2), (2048, 4096, 4096, 0),
+                                        # token tiles of 32, 96, 192 and 224 (the tokens divided evenly over the fewest tiles)
+                                        (129, 520, 256, 0), (20, 300, 512, 1), (90, 600, 256, 2), (380, 1000, 320, 2), (640, 3000, 512, 0)])
 def test_gemm_tensor_block_pairs(M, N, K, mode):
-    """The two-block kernel (cta_group::2): a pair covers 256 features x 256 tokens."""
+    """The two-block kernel (cta_group::2): a pair covers 256 features x a token tile of up to 256."""
     from mdma_b200 import ops_tensor
     ops = ops_mod()
     torch.manual_seed(M + N)
