@@ -528,3 +528,108 @@ def test_biases_and_another_gate_activation_are_options_of_the_parts(tmp_path, d
         for row, (r, c) in enumerate(zip(ref, cut)):
             assert np.abs(out[row] - r[c + step]).max() < tol
     eng.check_status()
+
+
+# ---- layers with different cache needs in one model: all keys, and windows of two widths ------------------------
+WINDOWS = (0, 40, 100)
+
+
+def register_toy_windowed():
+    """Three attention layers: the first reads every key, the others only the last 40 and the last 100.  Their
+    caches are three groups with storage of their own; the windowed groups give pages back while a sequence
+    grows.  An architecture registered from here, out of the built-in parts."""
+    from mdma_b200.config import Architecture
+    from mdma_b200.registry import ARCHITECTURES
+    from mdma_b200.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    def describe(c):
+        norm = lambda prefix: PartSpec("rmsnorm", dict(width=E, eps=c["eps"]), prefix=prefix)
+        pos = PartSpec("rotary", dict(head_dim=D, rotary_dim=D, theta=c["theta"], layout="split_half", scaling=None))
+        layers = []
+        for i, window in enumerate(WINDOWS):
+            p = f"l{i}."
+            layers.append(LayerSpec(
+                "prenorm", norm(p + "n1."),
+                PartSpec("attention", dict(hidden_size=E, num_heads=H, num_kv_heads=K, head_dim=D, scale=D ** -0.5,
+                                           window=window, position=pos), prefix=p + "attn."),
+                norm(p + "n2."), PartSpec("gated_mlp", dict(hidden_size=E, intermediate_size=F), prefix=p + "mlp.")))
+        return ModelSpec(hidden_size=E, vocab_size=V, max_positions=512,
+                         embedding=PartSpec("embedding", dict(vocab_size=V, width=E), prefix="emb."),
+                         layers=layers, schedule=[ScheduleEntry(i) for i in range(len(WINDOWS))], final_norm=norm("final."),
+                         lm_head=PartSpec("lm_head", dict(vocab_size=V, width=E), prefix="head."))
+
+    ARCHITECTURES.register("ToyWindowedLM", Architecture("ToyWindowedLM", lambda d: dict(d), describe), replace=True)
+
+
+def plain_toy_windowed(c, W, ids):
+    W = {k: v.double() for k, v in W.items()}
+    T = len(ids)
+    x = W["emb.weight"][torch.tensor(ids)]
+    inv = plain_inv_freq(D, c["theta"], None)
+    pos = torch.arange(T)
+    for i, window in enumerate(WINDOWS):
+        p = f"l{i}."
+        h = plain_rmsnorm(x, W[p + "n1.weight"], c["eps"])
+        q = plain_rope((h @ W[p + "attn.q_proj.weight"].t()).reshape(T, H, D), pos, inv, "split_half")
+        k = plain_rope((h @ W[p + "attn.k_proj.weight"].t()).reshape(T, K, D), pos, inv, "split_half")
+        v = (h @ W[p + "attn.v_proj.weight"].t()).reshape(T, K, D)
+        x = x + plain_attention(q, k, v, D ** -0.5, window) @ W[p + "attn.o_proj.weight"].t()
+        h = plain_rmsnorm(x, W[p + "n2.weight"], c["eps"])
+        x = x + plain_swiglu(h @ W[p + "mlp.gate_proj.weight"].t(), h @ W[p + "mlp.up_proj.weight"].t()) @ W[p + "mlp.down_proj.weight"].t()
+    return plain_rmsnorm(x, W["final.weight"], c["eps"]) @ W["head.weight"].t()
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 8e-2)])
+def test_layers_with_all_keys_and_with_windows_in_one_model(tmp_path, dtype, tol):
+    """Prompts of 330 and 75 tokens in pieces (200 + 66 + single tokens; 70 + single tokens), NaN in every cache row
+    nobody owns: logits against the plain implementation with the same windows; the windowed groups hold
+    only the pages their windows reach (and gave the others back while the sequence grew), the group of all keys
+    holds them all."""
+    register_toy_windowed()
+    from mdma_b200.engine import Engine, StepEntry
+    from mdma_b200.weights import write_random_model
+    cfg = dict(architectures=["ToyWindowedLM"], eps=1e-5, theta=10000.0)
+    d = write_random_model(str(tmp_path / "toy5"), cfg, 6, torch.bfloat16 if dtype == "bfloat16" else torch.float32, std=0.08)
+    W = {n: t.float() for n, t in jitter_norm_weights(d, 6).items()}
+    eng = Engine(d, dtype=dtype, max_batch=2, max_context=384, logit_rows=256)
+    groups = {g.need.window: g for g in eng.cache.groups}
+    assert sorted(groups) == [0, 40, 100] and all(len(g.sites) == 1 for g in groups.values())
+    gen = torch.Generator().manual_seed(4)
+    seqs = [torch.randint(0, V, (n,), generator=gen).tolist() for n in (330, 75)]
+    ref = [plain_toy_windowed(cfg, W, s).numpy() for s in seqs]
+    slots = [eng.acquire() for _ in seqs]
+    pos = [0, 0]
+    plan = [[200, 66] + [1] * 64, [70] + [1] * 5]            # tokens each request brings, step by step
+    for step in range(max(len(p) for p in plan)):
+        entries, places = [], []
+        for i in range(2):
+            if step < len(plan[i]):
+                n = plan[i][step]
+                want = sorted({0, n // 2, n - 1})
+                entries.append(StepEntry(slots[i], seqs[i][pos[i]:pos[i] + n], want))
+                places += [(i, pos[i] + w) for w in want]
+                pos[i] += n
+        eng.cache.poison_unused()
+        out = eng.step(entries).cpu().numpy()
+        want_rows = np.stack([ref[i][p] for i, p in places])
+        assert np.abs(out - want_rows).max() < tol, (step, np.abs(out - want_rows).max())
+    assert pos == [330, 75]
+    page = eng.cache.page_size
+    held = lambda window, slot: sorted(groups[window].seq_pages[slot])
+    assert held(0, slots[0]) == list(range(-(-330 // page)))
+    for window in (40, 100):
+        first = max(0, 330 - window) // page                 # the page of the earliest key the next token would read
+        assert held(window, slots[0]) == list(range(first, -(-330 // page))), (window, held(window, slots[0]))
+    eng.cache.check()
+    for s in slots:
+        eng.release(s)
+    eng.cache.check()
+    assert all(g.pages.free_count == g.n_pages for g in groups.values())
+    # and through the generation loop: replayed decode steps (graphs) equal the step-by-step loop while the
+    # windows move over page boundaries and pages are given back between runs
+    prompts = [s[:130] for s in seqs[:1]] + [seqs[1][:20]]
+    a = eng.generate(prompts, max_tokens=70)
+    b = eng.generate(prompts, max_tokens=70, use_graphs=False)
+    assert [o.tokens for o in a] == [o.tokens for o in b] and all(len(o.tokens) == 70 for o in a)
+    eng.cache.check()
+    eng.check_status()
