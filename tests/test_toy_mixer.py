@@ -532,11 +532,12 @@ def test_biases_and_another_gate_activation_are_options_of_the_parts(tmp_path, d
 
 # ---- layers with different cache needs in one model: all keys, and windows of two widths ------------------------
 WINDOWS = (0, 40, 100)
+GEOMETRY = ((H, K, D), (H, K, D), (2, 1, 32))        # heads, kv heads, head size of each layer: the last differs too
 
 
 def register_toy_windowed():
-    """Three attention layers: the first reads every key, the others only the last 40 and the last 100.  Their
-    caches are three groups with storage of their own; the windowed groups give pages back while a sequence
+    """Three attention layers: the first reads every key, the others only the last 40 and the last 100, and the
+    last has other heads (2 of 32 over 1 kv head).  Their caches are three groups with storage of their own; the windowed groups give pages back while a sequence
     grows.  An architecture registered from here, out of the built-in parts."""
     from mdma_b200.config import Architecture
     from mdma_b200.registry import ARCHITECTURES
@@ -544,13 +545,13 @@ def register_toy_windowed():
 
     def describe(c):
         norm = lambda prefix: PartSpec("rmsnorm", dict(width=E, eps=c["eps"]), prefix=prefix)
-        pos = PartSpec("rotary", dict(head_dim=D, rotary_dim=D, theta=c["theta"], layout="split_half", scaling=None))
         layers = []
-        for i, window in enumerate(WINDOWS):
+        for i, (window, (h, k, d)) in enumerate(zip(WINDOWS, GEOMETRY)):
             p = f"l{i}."
+            pos = PartSpec("rotary", dict(head_dim=d, rotary_dim=d, theta=c["theta"], layout="split_half", scaling=None))
             layers.append(LayerSpec(
                 "prenorm", norm(p + "n1."),
-                PartSpec("attention", dict(hidden_size=E, num_heads=H, num_kv_heads=K, head_dim=D, scale=D ** -0.5,
+                PartSpec("attention", dict(hidden_size=E, num_heads=h, num_kv_heads=k, head_dim=d, scale=d ** -0.5,
                                            window=window, position=pos), prefix=p + "attn."),
                 norm(p + "n2."), PartSpec("gated_mlp", dict(hidden_size=E, intermediate_size=F), prefix=p + "mlp.")))
         return ModelSpec(hidden_size=E, vocab_size=V, max_positions=512,
@@ -565,15 +566,15 @@ def plain_toy_windowed(c, W, ids):
     W = {k: v.double() for k, v in W.items()}
     T = len(ids)
     x = W["emb.weight"][torch.tensor(ids)]
-    inv = plain_inv_freq(D, c["theta"], None)
     pos = torch.arange(T)
-    for i, window in enumerate(WINDOWS):
+    for i, (window, (nh, nk, hd)) in enumerate(zip(WINDOWS, GEOMETRY)):
         p = f"l{i}."
+        inv = plain_inv_freq(hd, c["theta"], None)
         h = plain_rmsnorm(x, W[p + "n1.weight"], c["eps"])
-        q = plain_rope((h @ W[p + "attn.q_proj.weight"].t()).reshape(T, H, D), pos, inv, "split_half")
-        k = plain_rope((h @ W[p + "attn.k_proj.weight"].t()).reshape(T, K, D), pos, inv, "split_half")
-        v = (h @ W[p + "attn.v_proj.weight"].t()).reshape(T, K, D)
-        x = x + plain_attention(q, k, v, D ** -0.5, window) @ W[p + "attn.o_proj.weight"].t()
+        q = plain_rope((h @ W[p + "attn.q_proj.weight"].t()).reshape(T, nh, hd), pos, inv, "split_half")
+        k = plain_rope((h @ W[p + "attn.k_proj.weight"].t()).reshape(T, nk, hd), pos, inv, "split_half")
+        v = (h @ W[p + "attn.v_proj.weight"].t()).reshape(T, nk, hd)
+        x = x + plain_attention(q, k, v, hd ** -0.5, window) @ W[p + "attn.o_proj.weight"].t()
         h = plain_rmsnorm(x, W[p + "n2.weight"], c["eps"])
         x = x + plain_swiglu(h @ W[p + "mlp.gate_proj.weight"].t(), h @ W[p + "mlp.up_proj.weight"].t()) @ W[p + "mlp.down_proj.weight"].t()
     return plain_rmsnorm(x, W["final.weight"], c["eps"]) @ W["head.weight"].t()
