@@ -480,9 +480,9 @@ attention_decode_kernel(const AttnParams p) {
 // stored as halves of 64 head elements: [KB keys x 128 bytes] with the 128-byte swizzle.
 // NW warps per block.  All blocks should run at once (a second, short round of blocks costs as
 // much as the first): eight warps and one block per SM while the blocks are no more than the SMs, else
-// four, three or two warps with three, four or five blocks per SM.
+// four, three or two warps with three, four or five blocks per SM, or one warp with ten.
 template <int DMAX, int KB, int NW>
-__global__ void __launch_bounds__(NW * 32, NW == 8 ? 1 : NW == 4 ? 3 : NW == 3 ? 4 : 5)
+__global__ void __launch_bounds__(NW * 32, NW == 8 ? 1 : NW == 4 ? 3 : NW == 3 ? 4 : NW == 2 ? 5 : 10)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const AttnParams p) {
     constexpr int kChunks = DMAX / 8;
@@ -920,23 +920,29 @@ static int launch_attention_mma(const void* q, int q_stride, const void* k_cache
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         // the most warps per block with which every block of the grid is resident at once
         const long blocks = (long)n_seqs * n_kv_heads * splits;
+        // (up to ten blocks per SM: one warp each.  128 sequences x 8 kv heads at context 580, with the rotary kernel
+        // before it: 64.0 us against 77.8 us in two and a bit rounds of four-warp blocks; 184 sequences 88.0 against
+        // 98.8 us.  Beyond that, rounds of four-warp blocks: 192 sequences 99.0 us against 110.7 us with one warp)
         const int nw = blocks <= sm_count ? 8 : blocks <= 3l * sm_count ? 4 : blocks <= 4l * sm_count ? 3 :
-                       blocks <= 5l * sm_count ? 2 : 4;
+                       blocks <= 5l * sm_count ? 2 : blocks <= 10l * sm_count ? 1 : 4;
         if (kb == 64) {
             rc = nw == 8 ? launch(attention_decode_tma_kernel<64, 64, 8>, 8, 64)
                : nw == 4 ? launch(attention_decode_tma_kernel<64, 64, 4>, 4, 64)
                : nw == 3 ? launch(attention_decode_tma_kernel<64, 64, 3>, 3, 64)
-                         : launch(attention_decode_tma_kernel<64, 64, 2>, 2, 64);
+               : nw == 2 ? launch(attention_decode_tma_kernel<64, 64, 2>, 2, 64)
+                         : launch(attention_decode_tma_kernel<64, 64, 1>, 1, 64);
         } else if (head_dim <= 64) {
             rc = nw == 8 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 8>, 8, 64)
                : nw == 4 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 4>, 4, 64)
                : nw == 3 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 3>, 3, 64)
-                         : launch(attention_decode_tma_kernel<64, kDecodeKeys, 2>, 2, 64);
+               : nw == 2 ? launch(attention_decode_tma_kernel<64, kDecodeKeys, 2>, 2, 64)
+                         : launch(attention_decode_tma_kernel<64, kDecodeKeys, 1>, 1, 64);
         } else {
             rc = nw == 8 ? launch(attention_decode_tma_kernel<128, kDecodeKeys, 8>, 8, 128)
                : nw == 4 ? launch(attention_decode_tma_kernel<128, kDecodeKeys, 4>, 4, 128)
                : nw == 3 ? launch(attention_decode_tma_kernel<128, kDecodeKeys, 3>, 3, 128)
-                         : launch(attention_decode_tma_kernel<128, kDecodeKeys, 2>, 2, 128);
+               : nw == 2 ? launch(attention_decode_tma_kernel<128, kDecodeKeys, 2>, 2, 128)
+                         : launch(attention_decode_tma_kernel<128, kDecodeKeys, 1>, 1, 128);
         }
         if (rc) return rc;
     } else if (max_new == 1 && p.group <= 16) {

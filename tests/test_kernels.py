@@ -302,13 +302,13 @@ class StepMeta:
                                            (6, 1, 80, 0), (8, 2, 128, 100), (5, 5, 112, 33), (32, 8, 128, 0),
                                            (40, 2, 64, 0), (64, 1, 32, 0)])      # groups of 20 and 64 query heads
 @pytest.mark.parametrize("case", ["prefill", "chunked", "decode", "decode_split", "decode_long", "decode_many1",
-                                  "decode_many3", "decode_many4", "decode_page16", "prefill_tc", "chunked_tc"])
+                                  "decode_many3", "decode_many4", "decode_many5", "decode_page16", "prefill_tc", "chunked_tc"])
 @pytest.mark.parametrize("poison", [False, True])
 def test_attention_tensor(H, K, hd, window, case, poison):
     """The tensor-core attention against the float64 statement of the reference's loop:
     whole prompts, prompts on top of a cached prefix, single tokens (one block of eight warps; keys
     split over blocks, by hand and by the kernel's own choice for a long context; so many sequences
-    that blocks of four, three and two warps are taken; pages that the tile loads cannot use), with and
+    that blocks of four, three and two warps and of one warp are taken; pages that the tile loads cannot use), with and
     without NaN in every cache row that belongs to nobody."""
     from mdma_b200 import ops_tensor
     torch.manual_seed(H * 1000 + hd)
@@ -323,7 +323,7 @@ def test_attention_tensor(H, K, hd, window, case, poison):
         cached, new = [2500, 1030, 7], [1, 1, 1]          # beyond 1024: the kernel splits the keys itself
     elif case.startswith("decode_many"):
         sms = torch.cuda.get_device_properties(0).multi_processor_count
-        n = -(-int(case[-1]) * sms // K) + 1              # sequences x kv heads just beyond 1, 3, 4 x SMs: blocks of 4, 3, 2 warps
+        n = -(-int(case[-1]) * sms // K) + 1              # sequences x kv heads just beyond 1, 3, 4, 5 x SMs: blocks of 4, 3, 2 warps, 1 warp
         g = torch.Generator().manual_seed(7)
         cached, new = torch.randint(0, 150, (n,), generator=g).tolist(), [1] * n
     else:
