@@ -198,15 +198,17 @@ def test_decoding_across_the_1024_bucket(dtype):
     check_rows(got, index, ref, dtype, "across 1,024")
 
 
+@pytest.mark.parametrize("n_requests", [48, 100, 140])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_a_batch_of_48_sequences(dtype):
-    """48 short requests with 8 kv heads: sequences x kv heads = 384 is at least twice the number of
-    multiprocessors, where the decode attention takes blocks of four warps without a split."""
+def test_a_batch_of_many_sequences(dtype, n_requests):
+    """48, 100 and 140 short requests with 8 kv heads: sequences x kv heads = 384 is at least twice the number of
+    multiprocessors, where the decode attention takes blocks of fewer warps without a split; 800 is more than five
+    times (blocks of one warp); with 140 the step has more than 128 tokens (other kernels for the products)."""
     cfg = TINY_D
     d, c, tensors = make_model(cfg, 3, torch.bfloat16, std_scale=SHARP)
     V = cfg["vocab_size"]
     g = torch.Generator().manual_seed(50)
-    lengths = torch.randint(8, 70, (48,), generator=g).tolist()
+    lengths = torch.randint(8, 70, (n_requests,), generator=g).tolist()
     reqs = requests_for(cfg, 51, lengths)
     ref = {rid: oracle(c, tensors, ids, dtype) for rid, ids in reqs.items()}
     steps = [{"entries": [{"id": rid, "tokens": ids[:-6], "want": [len(ids) - 7]} for rid, ids in reqs.items()], "end": []}]
@@ -215,8 +217,8 @@ def test_a_batch_of_48_sequences(dtype):
         steps.append({"entries": [{"id": rid, "tokens": [ids[-j]], "want": [0]} for rid, ids in reqs.items()],
                       "end": list(reqs) if j == 1 else []})
         index.append([(rid, len(ids) - j) for rid, ids in reqs.items()])
-    got = replay(d, dtype, steps, max_tokens=48 * 128, vocab=V, extra_args=("--poison-unused",))
-    check_rows(got, index, ref, dtype, "48 sequences")
+    got = replay(d, dtype, steps, max_tokens=n_requests * 128, vocab=V, extra_args=("--poison-unused",))
+    check_rows(got, index, ref, dtype, f"{n_requests} sequences")
 
 
 def test_first_tokens_and_long_decoding():
