@@ -18,7 +18,7 @@ EVEN_SPLIT = os.environ.get("MDMA_EVEN_SPLIT", "1") != "0"
 
 FORCED_ATTENTION = os.environ.get("MDMA_ATTN")        # "tc" or "mma": one attention kernel for every step (comparisons)
 
-PAIR_TOKENS = 128        # steps of more tokens than this run on the block-pair kernel
+PAIR_TOKENS = 96         # steps of more tokens than this may run a product on the block-pair kernel (the gated one from 97)
 
 
 def pair_scratch_floats(sms: int) -> int:
