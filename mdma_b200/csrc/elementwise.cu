@@ -579,7 +579,10 @@ int mdma_rope_cache_write(void* qkv, int dtype, int row_stride, const float* par
         MDMA_LAUNCH_OK("rope_cache_write");
         return 0;
     }
-    if (splits > 0 && dtype == kBF16 && rotary_dim % 8 == 0 && head_dim % 8 == 0 && row_stride % 4 == 0 &&
+    // (from 65 tokens: alone it is faster from 32 on, but in a decode step's chain of kernels a layer of 32 or 64
+    // sequences took 117.0 and 141.0 us with it against 113.5 and 137.1 us with the many small blocks of the scalar
+    // kernel; 80 sequences 147.9 against 150.0 us, 128 sequences 176.5 against 179.0 us)
+    if (n_tokens > 64 && splits > 0 && dtype == kBF16 && rotary_dim % 8 == 0 && head_dim % 8 == 0 && row_stride % 4 == 0 &&
         partial_width % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)partial & 15) == 0 && ((uintptr_t)qkv & 7) == 0 &&
         (!write_kv || (((uintptr_t)k_cache & 7) == 0 && ((uintptr_t)v_cache & 7) == 0))) {
         // partial sums with 16-byte loads; about two blocks per SM
