@@ -846,6 +846,11 @@ int mdma_gemm_tc_plan(int mode, int n_tokens, int n_features, int K, int sm_coun
         // slower again), one per SM for larger tiles, which take the whole shared memory (128 tokens:
         // QKV 14.5 us with 3 splits against 21.8 us with 6, O 12.3 against 19.5, down 26.9 against 34.8).
         splits = (int)(((bn <= 64 ? 2 : 1) * sm_count) / tiles);
+        // A product that is stored (QKV) is followed by a kernel on the critical path that adds its partial sums
+        // up itself (the decode attention with the rotary encoding inside, or the rotary kernel): fewer, 5/4 blocks
+        // per SM.  Measured in the layer chain at the 8B shape, 4 splits against 6: batch 1 88.8 against 90.3 us,
+        // batch 4 91.7 against 94.1, batch 8 93.5 against 95.6, batch 16 97.6 against 100.0; batch 32 and 64 the same.
+        if (mode == kTcStore && bn <= 64) splits = (int)((5L * sm_count / 4 + tiles - 1) / tiles);
         if (splits < 1) splits = 1;
         if (splits > 16) splits = 16;
         if (splits > k_blocks / 4) splits = k_blocks / 4 > 0 ? k_blocks / 4 : 1;
