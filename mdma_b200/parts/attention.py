@@ -146,15 +146,17 @@ class Attention(Part):
 
     def _fusable(self, ctx, view) -> bool:
         """Whether this step's attention kernel should do the position encoding and the cache write
-        itself.  It pays while every (sequence, kv head) has a block of eight warps to itself (measured at
-        the 8B layer shape: the chain of a layer takes 93.6 us against 96.4 us at batch 8, but 139 us
-        against 135 us at batch 64, where each of many small blocks repeats the work on the projection
-        row).  MDMA_FUSED_ROTARY=0 turns it off, for comparisons."""
+        itself.  It pays while the kernel's blocks have three warps or more (up to four blocks per SM).  Measured
+        at the 8B layer shape, the chain of a layer with and without: batch 8 93.6 against 96.4 us; batch 32
+        112.7 against 113.5, batch 64 136.6 against 138.2 (with the QKV product split four ways; with six it was
+        the other way round, because every block adds up the projection's partial rows itself); batch 96 173.9
+        against 163.3, batch 128 187.9 against 176.6 (blocks of one or two warps).  MDMA_FUSED_ROTARY=0 turns it
+        off, for comparisons."""
         if self.rt.attention != "fast" or not hasattr(self.position, "rotary_table") or not FUSED_ROTARY:
             return False
         from .. import ops_tensor
         sms = self.rt.tc.sms if self.rt.tc is not None else 0
-        return (ctx.n_seqs * self.n_kv_heads <= sms and
+        return (ctx.n_seqs * self.n_kv_heads <= 4 * sms and
                 ops_tensor.fused_rotary_supported(self.n_heads, self.n_kv_heads, self.head_dim, view.page_size,
                                                   self.position.rotary_table()[1]))
 
