@@ -30,6 +30,10 @@ constexpr int kBM = 128;        // features per tile (MMA M)
 constexpr int kBK = 64;         // K per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kTcThreads = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+// Token tiles of 64 and more have eight epilogue warps, two per 32 rows, each with half of the columns: a block of such
+// a tile has its SM to itself (or shares it with one other), so nothing else hides the time it takes to read the
+// accumulators out.
+template <int BN> constexpr int tc_threads() { return BN >= 64 ? 320 : kTcThreads; }
 constexpr int kTc2Threads = 320; // block-pair kernel: warps 2-9 are the epilogue, two warps (column halves) per 32 lanes of tensor memory
 
 struct TcParams {
@@ -58,7 +62,7 @@ struct TcSmem {
 };
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(kTcThreads)
+__global__ void __launch_bounds__(tc_threads<BN>())
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     using S = TcSmem<BN, MODE>;
@@ -163,6 +167,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // ---- epilogue: TMEM -> registers -> (cluster reduction) -> global ------------------
     const int quad = warp & 3;                  // the TMEM lanes an epilogue warp may read
     const int f = f0 + quad * 32 + lane;
+    constexpr int kColsPerWarp = BN >= 64 ? BN / 2 : BN;                 // eight epilogue warps: column halves
+    const int c_lo = BN >= 64 ? ((warp - 2) >> 2) * kColsPerWarp : 0, c_hi = c_lo + kColsPerWarp;
     bool acc_ok = false;
     if (warp >= 2) {
         chain_wait();                           // the output may still be read by an earlier kernel
@@ -180,7 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint32_t slot = ptx::cluster_map(base, 0) +
                                   (uint32_t)(((rank - 1) * kAccs * BN) * kBM + quad * 32 + lane) * 4u;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
+            for (int c = c_lo; c < c_hi; c += 16) {
                 if (t0 + c >= p.n_tokens) break;
                 float v[16], u[16];
                 if (acc_ok) {
@@ -207,7 +213,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const float b1 = biased ? ending_bias(p.ending.bias, p.ending.bias_dtype, f) : 0.f;
         const float b2 = kDual && biased ? ending_bias(p.ending.bias2, p.ending.bias_dtype, f) : 0.f;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
+        for (int c = c_lo; c < c_hi; c += 16) {
             if (t0 + c >= p.n_tokens) break;           // uniform over the warp
             float v[16], u[16];
             if (acc_ok) {
@@ -677,7 +683,7 @@ static int run_tc(const void* x, int ldx, const void* w, const void* w2, int K, 
     if (p.cluster > 1) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(((p.n_features + kBM - 1) / kBM) * p.cluster, (p.n_tokens + BN - 1) / BN, 1);
-        cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = S::kBytes; cfg.stream = stream;
+        cfg.blockDim = dim3(tc_threads<BN>()); cfg.dynamicSmemBytes = S::kBytes; cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = p.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
@@ -689,7 +695,7 @@ static int run_tc(const void* x, int ldx, const void* w, const void* w2, int K, 
         return 0;
     }
     dim3 grid((p.n_features + kBM - 1) / kBM, (p.n_tokens + BN - 1) / BN, splits);
-    launch_chained(gemm_tc_kernel<BN, MODE>, grid, dim3(kTcThreads), S::kBytes, stream, mw, mw2, mx, p);
+    launch_chained(gemm_tc_kernel<BN, MODE>, grid, dim3(tc_threads<BN>()), S::kBytes, stream, mw, mw2, mx, p);
     MDMA_LAUNCH_OK("gemm_tc");
     return 0;
 }
