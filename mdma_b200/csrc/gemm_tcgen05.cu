@@ -33,7 +33,7 @@ constexpr int kTcThreads = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: e
 // Token tiles of 64 and more have eight epilogue warps, two per 32 rows, each with half of the columns: a block of such
 // a tile has its SM to itself (or shares it with one other), so nothing else hides the time it takes to read the
 // accumulators out.
-template <int BN> constexpr int tc_threads() { return BN >= 64 ? 320 : kTcThreads; }
+template <int BN> constexpr int tc_threads() { return BN >= 32 ? 320 : kTcThreads; }
 constexpr int kTc2Threads = 320; // block-pair kernel: warps 2-9 are the epilogue, two warps (column halves) per 32 lanes of tensor memory
 
 struct TcParams {
@@ -167,8 +167,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // ---- epilogue: TMEM -> registers -> (cluster reduction) -> global ------------------
     const int quad = warp & 3;                  // the TMEM lanes an epilogue warp may read
     const int f = f0 + quad * 32 + lane;
-    constexpr int kColsPerWarp = BN >= 64 ? BN / 2 : BN;                 // eight epilogue warps: column halves
-    const int c_lo = BN >= 64 ? ((warp - 2) >> 2) * kColsPerWarp : 0, c_hi = c_lo + kColsPerWarp;
+    constexpr int kColsPerWarp = BN >= 32 ? BN / 2 : BN;                 // eight epilogue warps: column halves
+    const int c_lo = BN >= 32 ? ((warp - 2) >> 2) * kColsPerWarp : 0, c_hi = c_lo + kColsPerWarp;
     bool acc_ok = false;
     if (warp >= 2) {
         chain_wait();                           // the output may still be read by an earlier kernel
