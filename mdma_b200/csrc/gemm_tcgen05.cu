@@ -33,7 +33,7 @@ constexpr int kTcThreads = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: e
 // Token tiles of 64 and more have eight epilogue warps, two per 32 rows, each with half of the columns: a block of such
 // a tile has its SM to itself (or shares it with one other), so nothing else hides the time it takes to read the
 // accumulators out.
-template <int BN> constexpr int tc_threads() { return BN >= 32 ? 320 : kTcThreads; }
+template <int BN> constexpr int tc_threads() { return 320; }
 constexpr int kTc2Threads = 320; // block-pair kernel: warps 2-9 are the epilogue, two warps (column halves) per 32 lanes of tensor memory
 
 struct TcParams {
@@ -167,8 +167,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // ---- epilogue: TMEM -> registers -> (cluster reduction) -> global ------------------
     const int quad = warp & 3;                  // the TMEM lanes an epilogue warp may read
     const int f = f0 + quad * 32 + lane;
-    constexpr int kColsPerWarp = BN >= 32 ? BN / 2 : BN;                 // eight epilogue warps: column halves
-    const int c_lo = BN >= 32 ? ((warp - 2) >> 2) * kColsPerWarp : 0, c_hi = c_lo + kColsPerWarp;
+    constexpr int kColsPerWarp = BN / 2;                                 // eight epilogue warps: column halves
+    constexpr int kStep = kColsPerWarp < 16 ? 8 : 16;                    // columns read out of tensor memory at a time
+    const int c_lo = ((warp - 2) >> 2) * kColsPerWarp, c_hi = c_lo + kColsPerWarp;
+    auto load_cols = [](uint32_t addr, float* dst) { if (kStep == 16) ptx::tmem_load_16(addr, dst); else ptx::tmem_load_8(addr, dst); };
     bool acc_ok = false;
     if (warp >= 2) {
         chain_wait();                           // the output may still be read by an earlier kernel
@@ -186,18 +188,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint32_t slot = ptx::cluster_map(base, 0) +
                                   (uint32_t)(((rank - 1) * kAccs * BN) * kBM + quad * 32 + lane) * 4u;
 #pragma unroll 1
-            for (int c = c_lo; c < c_hi; c += 16) {
+            for (int c = c_lo; c < c_hi; c += kStep) {
                 if (t0 + c >= p.n_tokens) break;
                 float v[16], u[16];
                 if (acc_ok) {
-                    ptx::tmem_load_16(lane_addr + c, v);
-                    if (kDual) ptx::tmem_load_16(lane_addr + BN + c, u);
+                    load_cols(lane_addr + c, v);
+                    if (kDual) load_cols(lane_addr + BN + c, u);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) { v[j] = 0.f; u[j] = 0.f; }
+                    for (int j = 0; j < kStep; ++j) { v[j] = 0.f; u[j] = 0.f; }
                 }
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < kStep; ++j) {
                     ptx::cluster_store_f32(slot + (uint32_t)((c + j) * kBM) * 4u, v[j]);
                     if (kDual) ptx::cluster_store_f32(slot + (uint32_t)((BN + c + j) * kBM) * 4u, u[j]);
                 }
@@ -213,36 +215,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const float b1 = biased ? ending_bias(p.ending.bias, p.ending.bias_dtype, f) : 0.f;
         const float b2 = kDual && biased ? ending_bias(p.ending.bias2, p.ending.bias_dtype, f) : 0.f;
 #pragma unroll 1
-        for (int c = c_lo; c < c_hi; c += 16) {
+        for (int c = c_lo; c < c_hi; c += kStep) {
             if (t0 + c >= p.n_tokens) break;           // uniform over the warp
             float v[16], u[16];
             if (acc_ok) {
-                ptx::tmem_load_16(lane_addr + c, v);
-                if (kDual) ptx::tmem_load_16(lane_addr + BN + c, u);
+                load_cols(lane_addr + c, v);
+                if (kDual) load_cols(lane_addr + BN + c, u);
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) { v[j] = 0.f; u[j] = 0.f; }
+                for (int j = 0; j < kStep; ++j) { v[j] = 0.f; u[j] = 0.f; }
             }
             for (int r = 1; r < p.cluster; ++r) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < kStep; ++j) {
                     v[j] += staged[(size_t)(((r - 1) * kAccs * BN) + c + j) * kBM];
                     if (kDual) u[j] += staged[(size_t)(((r - 1) * kAccs * BN) + BN + c + j) * kBM];
                 }
             }
             if (f < p.n_features) {
-                const int valid = min(16, p.n_tokens - (t0 + c));
+                const int valid = min(kStep, p.n_tokens - (t0 + c));
                 if (MODE == kTcAccumulate) {
                     // read the 16 residual values first so the loads overlap, then add and store
                     float* o = reinterpret_cast<float*>(p.out) + (size_t)(t0 + c) * p.ldo + f;
                     float old[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) old[j] = j < valid ? o[(size_t)j * p.ldo] : 0.f;
+                    for (int j = 0; j < kStep; ++j) old[j] = j < valid ? o[(size_t)j * p.ldo] : 0.f;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) if (j < valid) o[(size_t)j * p.ldo] = old[j] + (v[j] + b1);
+                    for (int j = 0; j < kStep; ++j) if (j < valid) o[(size_t)j * p.ldo] = old[j] + (v[j] + b1);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < kStep; ++j) {
                         if (j >= valid) break;
                         const int t = t0 + c + j;
                         float r = v[j] + b1;
