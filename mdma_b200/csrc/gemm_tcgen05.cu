@@ -34,7 +34,10 @@ constexpr int kTcThreads = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: e
 // a tile has its SM to itself (or shares it with one other), so nothing else hides the time it takes to read the
 // accumulators out.
 template <int BN> constexpr int tc_threads() { return 320; }
-constexpr int kTc2Threads = 320; // block-pair kernel: warps 2-9 are the epilogue, two warps (column halves) per 32 lanes of tensor memory
+// block-pair kernel: warps 2 and up are the epilogue, two warps (column halves) per 32 lanes of tensor memory, four
+// (column quarters) for the gated product, whose single accumulator buffer leaves the epilogue exposed
+template <int MODE> constexpr int tc2_epi_warps() { return MODE == 2 ? 16 : 8; }
+template <int MODE> constexpr int tc2_threads() { return (2 + tc2_epi_warps<MODE>()) * 32; }
 
 struct TcParams {
     void* out; int ldo; int out_f32;
@@ -335,7 +338,7 @@ __device__ inline PairWork pair_work(int pair, int n_pairs, int n_tiles, int n_k
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(kTc2Threads)
+__global__ void __launch_bounds__(tc2_threads<MODE>())
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                 const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     // Persistent: the grid holds at most one pair per two SMs and every pair walks over its segments.
@@ -374,8 +377,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     // nothing against its run time.
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(acc_full(b), 1); ptx::mbar_init(acc_empty(b), 16); }   // 8 epilogue warps x 2 blocks
-        ptx::mbar_init(ep_bar, 256);
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(acc_full(b), 1); ptx::mbar_init(acc_empty(b), 2 * tc2_epi_warps<MODE>()); }   // epilogue warps x 2 blocks
+        ptx::mbar_init(ep_bar, 32 * tc2_epi_warps<MODE>());
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -449,7 +452,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // ---- epilogue: each block handles its own 128 features x 256 tokens of every segment ------
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                   // feature row within this block's half
-        const int c_begin = ((warp - 2) >> 2) * (bn / 2), c_end = c_begin + bn / 2;     // this warp's columns
+        constexpr int kParts = tc2_epi_warps<MODE>() / 4;                              // column parts: halves or quarters
+        const int c_begin = ((warp - 2) >> 2) * (bn / kParts), c_end = c_begin + bn / kParts;     // this warp's columns
         const uint32_t lead_empty[2] = {ptx::cluster_map(acc_empty(0), 0), ptx::cluster_map(acc_empty(1), 0)};
         // partial tiles in global memory: [pair][block of the pair][accumulator][column][128 rows]
         const size_t part_stride = (size_t)kAccs * BN * 128;
@@ -719,7 +723,9 @@ static int run_tc2(const void* x, int ldx, const void* w, const void* w2, int K,
     // token tiles of up to 256, all of one width: the tokens divided evenly over the fewest tiles (320 tokens: two
     // tiles of 160, not one of 256 and one that is three quarters empty)
     const int t_tiles = (p.n_tokens + 255) / 256;
-    p.pair_tokens = (((p.n_tokens + t_tiles - 1) / t_tiles) + 31) / 32 * 32;
+    // (a multiple of 16 columns for every epilogue warp: 32 with column halves, 64 with quarters)
+    constexpr int kGrain = 16 * (tc2_epi_warps<MODE>() / 4);
+    p.pair_tokens = (((p.n_tokens + t_tiles - 1) / t_tiles) + kGrain - 1) / kGrain * kGrain;
     if (int rc = make_map_2d(&mx, x, (uint64_t)p.n_tokens, (uint64_t)K, (uint64_t)ldx * 2, p.pair_tokens / 2)) return rc;
     p.cluster = 1;
     cudaLaunchConfig_t cfg = {};
@@ -734,7 +740,7 @@ static int run_tc2(const void* x, int ldx, const void* w, const void* w2, int K,
     const long tiles = (long)((p.n_features + 255) / 256) * ((p.n_tokens + p.pair_tokens - 1) / p.pair_tokens);
     const int pairs = (int)(tiles < sm_count / 2 ? tiles : sm_count / 2);
     cfg.gridDim = dim3(pairs * 2, 1, 1);
-    cfg.blockDim = dim3(kTc2Threads); cfg.dynamicSmemBytes = S::kBytes; cfg.stream = stream;
+    cfg.blockDim = dim3(tc2_threads<MODE>()); cfg.dynamicSmemBytes = S::kBytes; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
