@@ -33,7 +33,8 @@ constexpr int kTcThreads = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: e
 // Token tiles of 64 and more have eight epilogue warps, two per 32 rows, each with half of the columns: a block of such
 // a tile has its SM to itself (or shares it with one other), so nothing else hides the time it takes to read the
 // accumulators out.
-template <int BN> constexpr int tc_threads() { return 320; }
+template <int BN> constexpr int tc_epi_parts() { return BN >= 128 ? 4 : 2; }         // epilogue warps per 32 rows
+template <int BN> constexpr int tc_threads() { return (2 + 4 * tc_epi_parts<BN>()) * 32; }
 // block-pair kernel: warps 2 and up are the epilogue, two warps (column halves) per 32 lanes of tensor memory, four
 // (column quarters) for the gated product, whose single accumulator buffer leaves the epilogue exposed
 template <int MODE> constexpr int tc2_epi_warps() { return MODE == 2 ? 16 : 8; }
@@ -170,7 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // ---- epilogue: TMEM -> registers -> (cluster reduction) -> global ------------------
     const int quad = warp & 3;                  // the TMEM lanes an epilogue warp may read
     const int f = f0 + quad * 32 + lane;
-    constexpr int kColsPerWarp = BN / 2;                                 // eight epilogue warps: column halves
+    constexpr int kColsPerWarp = BN / tc_epi_parts<BN>();                // eight epilogue warps: column halves (sixteen: quarters)
     constexpr int kStep = kColsPerWarp < 16 ? 8 : 16;                    // columns read out of tensor memory at a time
     const int c_lo = ((warp - 2) >> 2) * kColsPerWarp, c_hi = c_lo + kColsPerWarp;
     auto load_cols = [](uint32_t addr, float* dst) { if (kStep == 16) ptx::tmem_load_16(addr, dst); else ptx::tmem_load_8(addr, dst); };
