@@ -128,6 +128,14 @@ def _gemm_plan(mode: int, n_tokens: int, n_features: int, k: int, sms: int) -> t
     return bn.value, splits.value
 
 
+def gemm_scratch_floats(bn: int, splits: int, m: int, n: int, sms: int) -> int:
+    """Floats of scratch a product of m tokens x n features needs with this token tile and K split: the partial
+    sums of a split through global memory, or the partial tiles of the block-pair kernel (`bn` 512)."""
+    if bn == 512:
+        return pair_scratch_floats(sms)
+    return splits * m * n if splits > 1 else 0
+
+
 class Pending:
     """Partial sums of a K-split product that still wait in the scratch to be added
     up into (or onto) `target`: [splits, rows, cols] floats."""
@@ -187,10 +195,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ops.GE
         pbn, psplits = gemm_plan(mode, M, N, K, st.sms)
         bn = bn or pbn
         splits = splits or psplits
-    need = splits * M * N if splits > 1 else 0
-    if bn == 512:
-        need = pair_scratch_floats(st.sms)      # partial tiles of the block-pair kernel's even K-block split
-    st.need(need, "a K-split product")
+    st.need(gemm_scratch_floats(bn, splits, M, N, st.sms), "a K-split product")
     used = ctypes.c_int(1)
     _call("tensor", "mdma_gemm_tc", _i(mode), _ptr(a), _i(a.stride(0)), _ptr(w), _ptr(w2), _ptr(out),
           _i(int(out.dtype == torch.float32)), _i(out.stride(0)), _i(M), _i(N), _i(K), _i(bn), _i(splits),
