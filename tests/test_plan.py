@@ -41,3 +41,28 @@ def test_choices_that_the_measurements_rest_on():
     assert plan(STORE, 256, 6144, 4096) == (128, 1)          # QKV stays unsplit there (its partial sums cost the rotary kernel more)
     assert plan(GATED, 2048, 14336, 4096) == (512, 1) and plan(STORE, 2048, 6144, 4096) == (512, 1)
     assert plan(STORE, 8, 128256, 4096) == (16, 1)           # the head: more tiles than SMs, no split
+
+
+@pytest.mark.parametrize("sms", [148, 78])
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(32, 8, 128), (32, 32, 128), (32, 8, 64), (16, 8, 16), (6, 3, 48), (64, 1, 32), (40, 2, 64)])
+def test_every_choice_of_key_splits_fits_the_scratch_reserved_for_attention(heads, kv_heads, head_dim, sms):
+    """The attention kernels keep tokens x heads x splits x (head_dim + 2) floats when they split the keys; the
+    engine reserves a bound computed from sizes alone.  Every (sequences, tokens per sequence, context, capacity)
+    the step function can see must stay below it."""
+    reserved = (ops_tensor.scratch_floats_bound(sms, 8192, 1, [(heads, kv_heads, head_dim)])
+                - ops_tensor.scratch_floats_bound(sms, 8192, 1, ()))
+    worst = 0
+    for n_seqs in list(range(1, 40)) + [48, 64, 100, 148, 200, 300, 600]:
+        for max_new in (1, 2, 5, 16, 17, 64, 129, 700):
+            if n_seqs * max_new > 8192:
+                continue
+            for max_len in (1, 64, 580, 1024, 1025, 4096, 40000):
+                if max_len < max_new:
+                    continue
+                for most in (None, n_seqs, max(n_seqs, 64)):
+                    splits = ops_tensor.attention_splits(n_seqs, max_new, max_len, heads, kv_heads, sms, most)
+                    assert 1 <= splits <= 32
+                    need = n_seqs * max_new * heads * splits * (head_dim + 2) if splits > 1 else 0
+                    worst = max(worst, need)
+                    assert need <= reserved, (n_seqs, max_new, max_len, most, splits, need, reserved)
+    assert worst > 0          # the sweep did reach split cases
