@@ -145,7 +145,7 @@ def plan_only(model_dir: str, dtype="bfloat16", max_batch: int = 1, max_context:
         stored = stored_dtypes(model_dir)
     except Exception:
         stored = None                       # a folder without weights can still be planned
-    chunk = max(1, min(chunk_tokens, max_tokens))
+    chunk = max(1, min(chunk_tokens, max_tokens), max_batch)
     carver = Carver()
     lay = lay_out(model, carver, dtype=_DTYPES[dtype], device="meta", sms=sms, max_tokens=max_tokens,
                   max_slots=max_batch, max_context=ctx, page_size=page_size, chunk_tokens=chunk,
@@ -194,7 +194,8 @@ class Engine:
         else:
             self.max_slots = max(1, min(-(-max_tokens // page_size), 4096))
         self.max_tokens = -(-int(max_tokens) // page_size) * page_size
-        self.chunk_tokens = max(1, min(int(chunk_tokens), self.max_tokens))
+        # a pass holds at least one token of every slot: the replayed decode step runs all live sequences at once
+        self.chunk_tokens = max(1, min(int(chunk_tokens), self.max_tokens), self.max_slots)
         self.logit_rows = max(1, int(logit_rows if logit_rows is not None else self.max_slots))
 
         if kernels == "auto":

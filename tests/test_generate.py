@@ -53,6 +53,21 @@ def test_generation_with_other_page_sizes(page):
     eng.cache.check()
 
 
+def test_a_pass_size_smaller_than_the_batch():
+    """An engine asked for passes of 16 tokens and 40 sequences: a decode step of 40 single tokens is one pass all
+    the same (the pass size is raised to the number of slots), prompts still run in several passes."""
+    from mdma_b200.engine import Engine
+    d, c, tensors = make_model(TINY_A, 0, torch.float32, std_scale=SHARP)
+    eng = Engine(d, dtype="float32", max_batch=40, max_context=64, chunk_tokens=16)
+    assert eng.chunk_tokens == 40
+    prompts = prompts_for(TINY_A, tuple(3 + i % 7 for i in range(40)), 9)
+    outs = eng.generate(prompts, max_tokens=5)
+    for p, o in zip(prompts[:6] + prompts[-3:], outs[:6] + outs[-3:]):
+        assert o.tokens == plain_generate(c, tensors, p, 5)
+    assert [o.tokens for o in outs] == [o.tokens for o in eng.generate(prompts, max_tokens=5, use_graphs=False)]
+    eng.cache.check()
+
+
 def test_batches_one_after_another_and_stop_tokens():
     import mdma_b200
     d, c, tensors = make_model(TINY_C, 2, torch.float32)
