@@ -196,7 +196,8 @@ class Engine:
         self.max_tokens = -(-int(max_tokens) // page_size) * page_size
         # a pass holds at least one token of every slot: the replayed decode step runs all live sequences at once
         self.chunk_tokens = max(1, min(int(chunk_tokens), self.max_tokens), self.max_slots)
-        self.logit_rows = max(1, int(logit_rows if logit_rows is not None else self.max_slots))
+        # (never fewer than the slots: the replayed decode step writes a row of logits per live sequence)
+        self.logit_rows = max(1, int(logit_rows if logit_rows is not None else self.max_slots), self.max_slots)
 
         if kernels == "auto":
             kernels = "tensor" if self.dtype == torch.bfloat16 else "plain"
